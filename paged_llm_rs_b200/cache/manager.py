@@ -24,7 +24,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from ..errors import CacheError
-from ..parts.base import PagedNeed, StateNeed
+from ..parts.base import CompositeNeed, PagedNeed, StateNeed
 from .allocator import BlockAllocator, block_hash
 
 FREED = -1  # a table entry whose page was given back (window groups only)
@@ -83,6 +83,8 @@ class CacheGroup:
     allocator: BlockAllocator
     page_size: int
     pool: Optional[torch.Tensor] = None  # need.pool_shape(entries, pages, page_size)
+    # per cache of the group, whose it is: the schedule entry, or (entry, part) for a part of a mixer made of several
+    cells: List[object] = field(default_factory=list)
 
     @property
     def window(self) -> Optional[int]:
@@ -112,33 +114,44 @@ class RequestCache:
 class CacheManager:
     def __init__(self, needs: Sequence[Optional[object]], page_size: int, num_pages: int, max_requests: int,
                  dtype: torch.dtype, device, prefix_cache: bool = True, allocate_device: bool = True):
-        """``needs[i]`` is what schedule entry i asks for (a PagedNeed, a StateNeed or None).
+        """``needs[i]`` is what schedule entry i asks for (a PagedNeed, a StateNeed, a CompositeNeed of those, or None).
         Every group gets ``num_pages`` pages of ``page_size`` tokens."""
         if page_size < 1:
             raise CacheError("page_size must be at least 1")
         self.page_size, self.num_pages, self.max_requests = page_size, num_pages, max_requests
         self.dtype, self.device = dtype, device
         self.groups: List[CacheGroup] = []
-        self._entry_group: Dict[int, Tuple[int, int]] = {}  # entry -> (group, index in group)
-        self._state_entries: Dict[int, StateNeed] = {}
+        # A cell is what one need gets: schedule entry i, or (i, j) for part j of an entry whose mixer is made of several
+        # (a CompositeNeed).
+        self._entry_group: Dict[object, Tuple[int, int]] = {}  # cell -> (group, index in group)
+        self._state_entries: Dict[object, StateNeed] = {}
+        self._composite: Dict[int, int] = {}                   # entry -> how many parts
         by_key: Dict[tuple, int] = {}
+        cells = []
         for i, need in enumerate(needs):
+            if isinstance(need, CompositeNeed):
+                self._composite[i] = len(need.parts)
+                cells += [((i, j), i, part) for j, part in enumerate(need.parts)]
+            else:
+                cells.append((i, i, need))
+        for cell, i, need in cells:
             if isinstance(need, PagedNeed):
                 key = need.group_key()
                 if key not in by_key:
                     by_key[key] = len(self.groups)
                     self.groups.append(CacheGroup(need, [], BlockAllocator(num_pages), page_size))
                 g = self.groups[by_key[key]]
-                self._entry_group[i] = (by_key[key], len(g.entries))
+                self._entry_group[cell] = (by_key[key], len(g.entries))
                 g.entries.append(i)
+                g.cells.append(cell)
             elif isinstance(need, StateNeed):
-                self._state_entries[i] = need
+                self._state_entries[cell] = need
             elif need is not None:
                 raise CacheError(f"schedule entry {i} asks for {need!r}, which the cache manager does not know")
         self._n_entries = len(needs)
         # state slots: one index per live request, shared by every entry that keeps state
         self._free_slots = list(range(max_requests - 1, -1, -1))
-        self._state: Dict[int, torch.Tensor] = {}
+        self._state: Dict[object, torch.Tensor] = {}
         self._requests: Dict[object, RequestCache] = {}
         # Sharing rests on pages that never change and are never dropped while held:
         # true for groups that keep every key, not for windows or state.
@@ -156,12 +169,15 @@ class CacheManager:
         """Per schedule entry what its mixer is handed: its view of the group's pool and the
         group's number ((k_pool, v_pool, group) for a KVNeed), a state tensor
         [max_requests, *shape], or None."""
-        out: List[object] = [None] * self._n_entries
-        for i, (gi, li) in self._entry_group.items():
+        by_cell: Dict[object, object] = {}
+        for cell, (gi, li) in self._entry_group.items():
             g = self.groups[gi]
-            out[i] = g.need.layer_view(g.pool, li) + (gi,) if g.pool is not None else (None, gi)
-        for i, t in self._state.items():
-            out[i] = t
+            by_cell[cell] = g.need.layer_view(g.pool, li) + (gi,) if g.pool is not None else (None, gi)
+        for cell, t in self._state.items():
+            by_cell[cell] = t
+        out: List[object] = [by_cell.get(i) for i in range(self._n_entries)]
+        for i, n in self._composite.items():
+            out[i] = tuple(by_cell.get((i, j)) for j in range(n))
         return out
 
     def bytes_per_token(self) -> int:

@@ -365,4 +365,49 @@ PLLM_EXPORT int pllm_swiglu(int dtype, const void* in, void* out, int n_rows, in
     return launch_status();
 }
 
+// The same with a bias on each half first: out = act(g + bias[c], u + bias[inter + c]); bias float [2 inter].
+template <typename T>
+__global__ void swiglu_bias_kernel(const T* in, const float* __restrict__ bias, T* __restrict__ out, int inter, long long total, int act,
+                                   float limit) {
+    pdl_launch_dependents();
+    pdl_wait(KID_SWIGLU);
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const long long row = idx / inter;
+        const int c = (int)(idx % inter);
+        const T* g = in + row * 2 * inter + c;
+        out[idx] = from_f32<T>(glu_act(act, limit, to_f32(g[0]) + bias[c], to_f32(g[inter]) + bias[inter + c]));
+    }
+}
+
+PLLM_EXPORT int pllm_swiglu_bias(int dtype, const void* in, const float* bias, void* out, int n_rows, int inter, int act, float limit,
+                                 cudaStream_t stream) {
+    if (n_rows <= 0) return PLLM_OK;
+    if (act < GLU_SILU || act > GLU_CLAMPED || inter <= 0 || bias == nullptr) return PLLM_ERR_SIZE;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        const long long total = (long long)n_rows * inter;
+        const int blocks = (int)min((long long)sm_count() * 16, (total + 255) / 256);
+        launch_chained(swiglu_bias_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)in, bias, (T*)out, inter, total, act, limit);
+    });
+    return launch_status();
+}
+
+// out = a * x + b * y, element by element, formed in float and rounded once (out may be x or y).
+template <typename T>
+__global__ void scaled_sum2_kernel(const T* x, const T* y, float a, float b, T* out, long long total) {
+    pdl_launch_dependents();
+    pdl_wait(KID_SWIGLU);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(a * to_f32(x[i]) + b * to_f32(y[i]));
+}
+
+PLLM_EXPORT int pllm_scaled_sum2(int dtype, const void* x, const void* y, float a, float b, void* out, long long total,
+                                 cudaStream_t stream) {
+    if (total <= 0) return PLLM_OK;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        const int blocks = (int)min((long long)sm_count() * 8, (total + 255) / 256);
+        launch_chained(scaled_sum2_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)x, (const T*)y, a, b, (T*)out, total);
+    });
+    return launch_status();
+}
+
 PLLM_TRACE_EXPORT(elementwise)

@@ -6,6 +6,7 @@
 //   round_rows          h = T(x)                                            (what a sublayer's products read)
 //   outnorm_add         x[r] += a[r] / sqrt(mean(a[r]^2) + eps) * gain;  h[r] = T(x[r])
 //                       (the norm sits on the sublayer's OUTPUT a, the sum stays in float)
+//   sandwich_norm32     x[r] += norm(a[r] + bias) * gain_a, then y[i] = T(norm(x[r]) * gain): output norm, sum and input norm
 //   rmsnorm_from32      y[i] = T(x[r] / sqrt(mean(x[r]^2) + eps) * gain),  r = rows ? rows[i] : i
 //   embed_norm32        x[t] = e / sqrt(mean(e^2) + eps) * gain,  e = table[token[t]]       (a norm right behind the embedding)
 //   add_scaled_norm32   x[r] += mult * d[r]  (d may be absent);  y[i] = T(x[r] / sqrt(mean(x[r]^2) + eps) * gain)
@@ -332,6 +333,104 @@ PLLM_EXPORT int pllm_add_scaled_norm32(int dtype, float* x, const void* d, float
         const int rows_per_cta = 8 / team;
         launch_chained(add_scaled_norm32_kernel<T>, dim3((n_rows + rows_per_cta - 1) / rows_per_cta), dim3(256), 0, stream, x,
                        (const T*)d, mult, gain, (T*)y, rows, n_rows, width, eps, team);
+    });
+    return launch_status();
+}
+
+// A block that norms each sublayer's input AND its output: the output's norm, the sum into the stream and the next
+// sublayer's input norm in one pass.  With a' = a + a_bias (a_bias may be null):
+//     x[r] += a'[r] / sqrt(mean(a'[r]^2) + eps) * gain_a                     (a given)
+//     y[i]  = T(x[r] / sqrt(mean(x[r]^2) + eps) * gain),  r = rows ? rows[i] : i     (y given)
+// The sum is stored only when every row is taken (rows null).  Rows and teams as in outnorm_add; a lane keeps up to
+// ADD_KEEP values of a row in registers and forms the others again.
+template <typename T>
+__global__ void __launch_bounds__(256) sandwich_norm32_kernel(float* x, const T* a, const float* __restrict__ a_bias,
+                                                              const float* __restrict__ gain_a, const float* __restrict__ gain,
+                                                              T* __restrict__ y, const int* __restrict__ rows, int n_rows, int width,
+                                                              float eps, int team) {
+    __shared__ float part[2][8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int member = (warp % team) * 32 + lane, lanes = team * 32;
+    const int rows_per_cta = 8 / team;
+    const int i = blockIdx.x * rows_per_cta + warp / team;
+    const int first = warp / team * team;
+    pdl_launch_dependents();
+    pdl_wait(KID_STREAM32);
+    const bool live = i < n_rows;
+    const size_t r = live ? (rows ? (size_t)rows[i] : (size_t)i) : 0;
+    float* xr = x + r * width;
+    const T* ar = a ? a + r * width : nullptr;
+    const bool store = a != nullptr && rows == nullptr;
+    float keep[ADD_KEEP];
+    float inv_a = 0.f;
+    if (a != nullptr) {
+        float ss = 0.f;
+        if (live) {
+            int k = 0;
+            for (int c = member; c < width; c += lanes, k++) {
+                float v = to_f32(ar[c]);
+                if (a_bias) v += a_bias[c];
+                if (k < ADD_KEEP) keep[k] = v;
+                ss += v * v;
+            }
+        }
+        ss = warp_sum(ss);
+        if (team > 1) {
+            if (lane == 0) part[0][warp] = ss;
+            __syncthreads();
+            ss = 0.f;
+            for (int w = 0; w < team; w++) ss += part[0][first + w];
+        }
+        inv_a = 1.0f / sqrtf(ss / (float)width + eps);
+    }
+    float ss = 0.f;
+    if (live) {
+        int k = 0;
+        for (int c = member; c < width; c += lanes, k++) {
+            float v = xr[c];
+            if (ar) {
+                float av;
+                if (k < ADD_KEEP) av = keep[k];
+                else { av = to_f32(ar[c]); if (a_bias) av += a_bias[c]; }
+                v += av * inv_a * gain_a[c];
+                if (store) xr[c] = v;
+            }
+            if (k < ADD_KEEP) keep[k] = v;
+            ss += v * v;
+        }
+    }
+    if (y == nullptr) return;
+    ss = warp_sum(ss);
+    if (team > 1) {
+        if (lane == 0) part[1][warp] = ss;
+        __syncthreads();
+        ss = 0.f;
+        for (int w = 0; w < team; w++) ss += part[1][first + w];
+    }
+    if (!live) return;
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    T* yr = y + (size_t)i * width;
+    int k = 0;
+    for (int c = member; c < width; c += lanes, k++) {
+        float v;
+        if (k < ADD_KEEP) v = keep[k];
+        else {
+            v = xr[c];
+            if (ar && !store) { float av = to_f32(ar[c]); if (a_bias) av += a_bias[c]; v += av * inv_a * gain_a[c]; }
+        }
+        yr[c] = from_f32<T>(v * inv * gain[c]);
+    }
+}
+
+PLLM_EXPORT int pllm_sandwich_norm32(int dtype, float* x, const void* a, const float* a_bias, const float* gain_a, const float* gain,
+                                     void* y, const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return PLLM_OK;
+    if (width <= 0 || (a != nullptr && gain_a == nullptr) || (y != nullptr && gain == nullptr)) return PLLM_ERR_SIZE;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        const int team = stream32_team(n_rows, width, 4);
+        const int rows_per_cta = 8 / team;
+        launch_chained(sandwich_norm32_kernel<T>, dim3((n_rows + rows_per_cta - 1) / rows_per_cta), dim3(256), 0, stream, x,
+                       (const T*)a, a_bias, gain_a, gain, (T*)y, rows, n_rows, width, eps, team);
     });
     return launch_status();
 }

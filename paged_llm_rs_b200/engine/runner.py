@@ -273,7 +273,7 @@ class ModelRunner:
         # a group whose mixers wish for nothing gets tables and slots only.
         plans = []
         for g in self.cache.groups:
-            wishes = {self.model.blocks[self.model.schedule[i].layer].mixer.plan_wish(page_size) for i in g.entries}
+            wishes = {self._mixer_of(cell).plan_wish(page_size) for cell in g.cells}
             if len(wishes) != 1:
                 raise ConfigError(f"the mixers that share a cache group wish for different attention plans: {sorted(map(str, wishes))}")
             w = wishes.pop()
@@ -296,6 +296,12 @@ class ModelRunner:
         self.tokens_host: Optional[torch.Tensor] = None   # pinned copy of the last step's (status, tokens), valid
                                                           # once the stream is synchronized; None: not made
         self.last_launches = 0    # kernels of this library the last step launched
+
+    def _mixer_of(self, cell):
+        """The mixer that a cache of a group belongs to: a schedule entry's, or part j of it for a cell (entry, j)."""
+        entry, part = cell if isinstance(cell, tuple) else (cell, None)
+        mixer = self.model.blocks[self.model.schedule[entry].layer].mixer
+        return mixer if part is None else mixer.parts[part]
 
     # -- the step ----------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry], check: bool = True, trace: Optional[dict] = None) -> torch.Tensor:

@@ -99,6 +99,18 @@ def lib():
         sig["pllm_attention_sink_mma"] = [P, P, P, P, P, c_int, P, P, P, P] + [c_int] * 9 + [c_float, c_float, P, P]
         sig["pllm_mamba2_mix"] = [c_int] + [P] * 8 + [c_int, c_int, P, c_ll, P, P, P] + [c_int] * 7 + [c_float, P]
         sig["pllm_pack_decode_step"] = [P, c_int, c_int, P, P, P, P, P] + [c_int] * 16 + [P, P]
+        sig["pllm_sandwich_norm32"] = [c_int, P, P, P, P, P, P, P, c_int, c_int, c_float, P]
+        sig["pllm_scaled_sum2"] = [c_int, P, P, c_float, c_float, P, c_ll, P]
+        sig["pllm_swiglu_bias"] = [c_int, P, P, P, c_int, c_int, c_int, c_float, P]
+        sig["pllm_normed_qk_kv_write"] = [c_int, P, c_int, c_int, c_int, P, P, P, c_int, c_float, c_float, c_int, P, c_int, P, P, P] + [c_int] * 7 + [c_ll, P, P]
+        sig["pllm_gate_mul"] = [c_int, P, P, c_int, c_int, c_int, c_int, P]
+        sig["pllm_mlstm_mix"] = [c_int, P, c_int, P, P, P, c_float, P, P, c_int, P, c_ll, P, P, P] + [c_int] * 4 + [c_float, P]
+        sig["pllm_delta_mix"] = [c_int, P, c_int, P, P, P, P, P, P, c_int, c_int, P, c_ll, P, P, P] + [c_int] * 6 + [c_float, P]
+        wide = {"pllm_mlstm_state_floats": [c_int] * 3, "pllm_delta_state_floats": [c_int] * 5}
+        for name, args in wide.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = c_ll
         for name, args in sig.items():
             fn = getattr(L, name)
             fn.argtypes = args
@@ -1083,4 +1095,181 @@ def mamba2_mix(u: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, dt_b
                                  _ptr(segments), segments.shape[0], int(max_segment_tokens), _ptr(state), state.stride(0),
                                  _ptr(c_buf), _ptr(y_buf), _ptr(out), T, heads, groups, vdim, n_state, taps, norm_groups,
                                  float(eps), _stream()), "mamba2_mix", launches=3)
+    return out
+
+
+# ---- a block that norms each sublayer's input and output, on a float32 stream (csrc/stream32.cu) ---------------------------
+
+def sandwich_norm32(x: torch.Tensor, a: Optional[torch.Tensor], a_bias: Optional[torch.Tensor], gain_a: Optional[torch.Tensor],
+                    gain: Optional[torch.Tensor], out: Optional[torch.Tensor], eps: float,
+                    rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """x (float32, in place) += norm(a + a_bias) * gain_a where a is given (a sublayer's output, normed before it is added);
+    out[i] = norm(x[r]) * gain where out is given (the next sublayer's input), r = rows[i] or i.  With ``rows`` the sum is
+    formed for those rows only and x is left as it is."""
+    _dev(x, a, a_bias, gain_a, gain, out, rows)
+    _f32(x, "x"); _f32(gain, "gain"); _f32(gain_a, "gain_a"); _f32(a_bias, "a_bias"); _i32(rows, "rows")
+    W = x.shape[-1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    if a is not None and (a.shape != x.shape or gain_a is None or gain_a.numel() != W or (a_bias is not None and a_bias.numel() != W)):
+        raise KernelError("sandwich_norm32: a must have x's shape, with a gain (and a bias, if any) of its width")
+    if out is not None and (out.shape != (n, W) or gain is None or gain.numel() != W or (a is not None and a.dtype != out.dtype)):
+        raise KernelError("sandwich_norm32: out or its gain does not fit")
+    if a is None and out is None:
+        return None
+    dtype = out.dtype if out is not None else a.dtype
+    _check(lib().pllm_sandwich_norm32(_code_of(dtype), _ptr(x), _ptr(a), _ptr(a_bias), _ptr(gain_a), _ptr(gain), _ptr(out), _ptr(rows),
+                                      n, W, float(eps), _stream()), "sandwich_norm32")
+    return out
+
+
+def swiglu_bias(gate_up: torch.Tensor, bias: torch.Tensor, out: torch.Tensor, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
+    """out[n, I] = act(gate_up[n, :I] + bias[:I], gate_up[n, I:] + bias[I:]); bias float32 [2 I]."""
+    _dev(gate_up, bias, out)
+    _f32(bias, "bias")
+    n, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (n, two_i // 2) or out.dtype != gate_up.dtype or bias.numel() != two_i:
+        raise KernelError("swiglu_bias: out must be [n, I] and bias [2 I] for an input [n, 2I] of out's dtype")
+    _check(lib().pllm_swiglu_bias(_code(gate_up), _ptr(gate_up), _ptr(bias), _ptr(out), n, two_i // 2, _glu(act), float(limit),
+                                  _stream()), "swiglu_bias")
+    return out
+
+
+def scaled_sum2(x: torch.Tensor, y: torch.Tensor, a: float, b: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a * x + b * y, formed in float and rounded once; ``out`` may be x or y (default: x)."""
+    out = x if out is None else out
+    _dev(x, y, out)
+    if y.shape != x.shape or y.dtype != x.dtype or out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("scaled_sum2: x, y and out must share one shape and dtype")
+    _check(lib().pllm_scaled_sum2(_code(x), _ptr(x), _ptr(y), float(a), float(b), _ptr(out), x.numel(), _stream()), "scaled_sum2")
+    return out
+
+
+# ---- queries and keys that are normed before the attention, and a gate behind it (csrc/normed_qk.cu) ---------------------------
+
+QK_NORMS = {None: 0, "head": 1, "projection": 2}
+
+
+def normed_qk_kv_write(proj: torch.Tensor, k_off: int, v_off: int, q_out: torch.Tensor, q_gain: Optional[torch.Tensor],
+                       k_gain: Optional[torch.Tensor], norm: Optional[str], eps: float, temp_coef: float, temp_every: int,
+                       inv_freq: Optional[torch.Tensor], rot: int, positions: torch.Tensor, slots: Optional[torch.Tensor],
+                       kv_pool: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, dk: int, dv: int, values_are_keys: bool,
+                       status: torch.Tensor) -> torch.Tensor:
+    """From a stacked projection ``proj`` [T, width] (q at 0, k at k_off, v at v_off) to the attention's inputs: q and k normed
+    (``norm``: None, "head": each head by its own root mean square with one gain of dk entries, "projection": all heads at
+    once with a gain of the projection's size), q times 1 + temp_coef ln(floor((p + 1) / temp_every) + 1) (temp_every 0:
+    not), both rotated on the first ``rot`` entries of each head; q to q_out [T, heads dk], k | v to row ``slots[t]`` of
+    kv_pool [pages, kv_heads, page_size, dk + dv].  ``values_are_keys``: v is the raw key projection (neither normed nor rotated)."""
+    _dev(proj, q_out, q_gain, k_gain, inv_freq, positions, slots, kv_pool, status)
+    _f32(q_gain, "q_gain"); _f32(k_gain, "k_gain"); _f32(inv_freq, "inv_freq"); _i32(positions, "positions"); _i32(slots, "slots")
+    T, width = proj.shape
+    if norm not in QK_NORMS:
+        raise KernelError(f"normed_qk_kv_write: norm {norm!r} is not known; known: {list(QK_NORMS)}")
+    if k_off + num_kv_heads * dk > width or (not values_are_keys and v_off + num_kv_heads * dv > width) or num_heads * dk > width:
+        raise KernelError("normed_qk_kv_write: the projection is narrower than its parts")
+    if q_out.numel() != T * num_heads * dk or q_out.dtype != proj.dtype:
+        raise KernelError("normed_qk_kv_write: q_out does not fit")
+    n_gain = {None: (0, 0), "head": (dk, dk), "projection": (num_heads * dk, num_kv_heads * dk)}[norm]
+    if norm is not None and (q_gain is None or k_gain is None or q_gain.numel() != n_gain[0] or k_gain.numel() != n_gain[1]):
+        raise KernelError("normed_qk_kv_write: the gains do not fit the norm")
+    if rot and (inv_freq is None or inv_freq.numel() * 2 != rot):
+        raise KernelError("normed_qk_kv_write: inv_freq must hold rot / 2 frequencies")
+    if positions.numel() < T or (slots is not None and slots.numel() < T):
+        raise KernelError("normed_qk_kv_write: positions / slots shorter than the tokens")
+    page_size, pool_rows = 1, 0
+    if kv_pool is not None:
+        if kv_pool.dim() != 4 or kv_pool.shape[1] != num_kv_heads or kv_pool.shape[3] != dk + dv or kv_pool.dtype != proj.dtype:
+            raise KernelError(f"normed_qk_kv_write: the pool must be [pages, {num_kv_heads}, page_size, {dk + dv}] of {proj.dtype}")
+        page_size, pool_rows = kv_pool.shape[2], kv_pool.shape[0] * kv_pool.shape[2]
+    _check(lib().pllm_normed_qk_kv_write(_code(proj), _ptr(proj), width, int(k_off), int(v_off), _ptr(q_out), _ptr(q_gain), _ptr(k_gain),
+                                         QK_NORMS[norm], float(eps), float(temp_coef), int(temp_every), _ptr(inv_freq), int(rot),
+                                         _ptr(positions), _ptr(slots), _ptr(kv_pool), T, num_heads, num_kv_heads, dk, dv,
+                                         1 if values_are_keys else 0, page_size, pool_rows, _ptr(status), _stream()),
+           "normed_qk_kv_write")
+    return q_out
+
+
+GATE_KINDS = {"sigmoid": 0, "silu": 1}
+
+
+def gate_mul(y: torch.Tensor, gate: torch.Tensor, kind: str = "sigmoid") -> torch.Tensor:
+    """y[t, c] *= sigmoid(gate[t, c]) (or silu), in place; ``gate`` may be a column range of a wider tensor."""
+    _dev(y)
+    if kind not in GATE_KINDS:
+        raise KernelError(f"gate_mul: kind {kind!r} is not known; known: {sorted(GATE_KINDS)}")
+    if not gate.is_cuda or gate.shape != y.shape or gate.dtype != y.dtype or gate.stride(1) != 1 or y.dim() != 2:
+        raise KernelError("gate_mul: the gate must have y's shape and dtype, with unit inner stride")
+    _check(lib().pllm_gate_mul(_code(y), _ptr(y), _ptr(gate), gate.stride(0), y.shape[0], y.shape[1], GATE_KINDS[kind], _stream()),
+           "gate_mul")
+    return y
+
+
+# ---- recurrent mixers with a matrix of state a head (csrc/matrix_memory.cu) ----------------------------------------------------
+
+def mlstm_state_floats(heads: int, dim: int, vdim: int) -> int:
+    """Floats of a request's state slot: every head's matrix, its normaliser vector and its running maximum."""
+    return heads * dim * vdim + heads * dim + heads
+
+
+def delta_state_floats(heads: int, kv_heads: int, dim: int, vdim: int, taps: int) -> int:
+    """Floats of a request's state slot: every head's matrix, then each channel's last taps - 1 inputs."""
+    return heads * dim * vdim + (taps - 1) * (2 * kv_heads * dim + heads * vdim)
+
+
+def _segments_ok(segments: torch.Tensor, what: str):
+    _i32(segments, "segments")
+    if segments.dim() != 2 or segments.shape[1] != 4:
+        raise KernelError(f"{what}: segments must be [n, 4]")
+
+
+def mlstm_mix(u: torch.Tensor, gates: torch.Tensor, i_bias: torch.Tensor, f_bias: torch.Tensor, cap: float, gain: torch.Tensor,
+              segments: torch.Tensor, state: torch.Tensor, out: torch.Tensor, heads: int, dim: int, vdim: int, eps: float) -> torch.Tensor:
+    """From the input projection's u [T, heads (2 dim + 2 vdim)] = [q | k | v | gate] and the gates' float32 projection
+    [T, 2 heads] = [i | f] to the output projection's input [T, heads vdim]: the matrix memory's recurrence over each
+    segment's tokens from and into its state slot, each head over its root mean square, the gain, sigmoid(gate)."""
+    _dev(u, gates, i_bias, f_bias, gain, segments, state, out)
+    for t, n in ((gates, "gates"), (i_bias, "i_bias"), (f_bias, "f_bias"), (gain, "gain"), (state, "state")):
+        _f32(t, n)
+    _segments_ok(segments, "mlstm_mix")
+    T = u.shape[0]
+    if u.shape != (T, heads * (2 * dim + 2 * vdim)) or out.shape != (T, heads * vdim) or out.dtype != u.dtype:
+        raise KernelError("mlstm_mix: u must be [T, heads (2 dim + 2 vdim)] and out [T, heads vdim] of one dtype")
+    if gates.shape != (T, 2 * heads) or min(i_bias.numel(), f_bias.numel()) != heads or gain.numel() != heads * vdim:
+        raise KernelError("mlstm_mix: gates must be [T, 2 heads], with a bias a head and gate, and a gain of heads vdim entries")
+    if state.dim() != 2 or state.shape[1] < mlstm_state_floats(heads, dim, vdim):
+        raise KernelError("mlstm_mix: the state slots are too small")
+    y_buf = torch.zeros((T, heads * vdim), dtype=torch.float32, device=u.device)     # (rows of no segment stay zero)
+    nm_buf = torch.empty((segments.shape[0], heads, dim + 1), dtype=torch.float32, device=u.device)
+    _check(lib().pllm_mlstm_mix(_code(u), _ptr(u), u.shape[1], _ptr(gates), _ptr(i_bias), _ptr(f_bias), float(cap), _ptr(gain),
+                                _ptr(segments), segments.shape[0], _ptr(state), state.stride(0), _ptr(nm_buf), _ptr(y_buf), _ptr(out), T,
+                                heads, dim, vdim, float(eps), _stream()), "mlstm_mix", launches=3)
+    return out
+
+
+def delta_mix(u: torch.Tensor, conv_w: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, gain: torch.Tensor,
+              segments: torch.Tensor, max_segment_tokens: int, state: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int,
+              dim: int, vdim: int, taps: int, eps: float) -> torch.Tensor:
+    """From the input projection's u [T, 2 kv_heads dim + 2 heads vdim] = [q | k | v | gate] and the float32 projection
+    ba [T, 2 heads] = [b | a] to the output projection's input [T, heads vdim]: convolution and silu, unit q and k, the
+    gated delta rule over each segment's tokens from and into its state slot, each head over its root mean square, the gain
+    (vdim entries, shared by the heads), silu(gate)."""
+    _dev(u, conv_w, ba, a_log, dt_bias, gain, segments, state, out)
+    for t, n in ((ba, "ba"), (a_log, "a_log"), (dt_bias, "dt_bias"), (gain, "gain"), (state, "state")):
+        _f32(t, n)
+    _segments_ok(segments, "delta_mix")
+    T = u.shape[0]
+    channels = 2 * kv_heads * dim + heads * vdim
+    if u.shape != (T, channels + heads * vdim) or out.shape != (T, heads * vdim) or out.dtype != u.dtype:
+        raise KernelError("delta_mix: u must be [T, 2 kv_heads dim + 2 heads vdim] and out [T, heads vdim] of one dtype")
+    if conv_w.shape != (channels, taps) or conv_w.dtype != u.dtype:
+        raise KernelError("delta_mix: the convolution's taps must be [channels, taps] of u's dtype")
+    if ba.shape != (T, 2 * heads) or min(a_log.numel(), dt_bias.numel()) != heads or gain.numel() != vdim:
+        raise KernelError("delta_mix: ba must be [T, 2 heads], with one A_log and dt_bias a head, and a gain of vdim entries")
+    if state.dim() != 2 or state.shape[1] < delta_state_floats(heads, kv_heads, dim, vdim, taps):
+        raise KernelError("delta_mix: the state slots are too small")
+    c_buf = torch.empty((T, channels), dtype=torch.float32, device=u.device)
+    y_buf = torch.zeros((T, heads * vdim), dtype=torch.float32, device=u.device)     # (rows of no segment stay zero)
+    _check(lib().pllm_delta_mix(_code(u), _ptr(u), u.shape[1], _ptr(conv_w), _ptr(ba), _ptr(a_log), _ptr(dt_bias), _ptr(gain),
+                                _ptr(segments), segments.shape[0], int(max_segment_tokens), _ptr(state), state.stride(0), _ptr(c_buf),
+                                _ptr(y_buf), _ptr(out), T, heads, kv_heads, dim, vdim, taps, float(eps), _stream()),
+           "delta_mix", launches=3)
     return out

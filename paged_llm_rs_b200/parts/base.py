@@ -169,6 +169,14 @@ class StateNeed:
 
 
 @dataclass(frozen=True)
+class CompositeNeed:
+    """What a mixer made of several mixers asks for: each part's need (a PagedNeed, a StateNeed or None), in the parts'
+    order.  The mixer is handed a tuple of what each part would have been handed alone."""
+
+    parts: Tuple[Optional[object], ...]
+
+
+@dataclass(frozen=True)
 class PlanWish:
     """What a mixer whose kernels read attention work items asks of the step packer: items of at
     most ``tile_tokens`` query tokens, for a kernel that launches ``ctas_per_item`` CTAs an item
@@ -290,7 +298,7 @@ class Mixer(Part):
     graph_safe = False
 
     def cache_need(self):
-        """KVNeed, StateNeed or None."""
+        """A PagedNeed, a StateNeed, a CompositeNeed of those, or None."""
         return None
 
     def plan_wish(self, page_size: int) -> Optional[PlanWish]:

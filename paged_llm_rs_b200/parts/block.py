@@ -77,6 +77,39 @@ class PreNormStreamBlock(Block):
         return self.post_mixer(stream, a, step)
 
 
+class SandwichStreamBlock(Block):
+    """x + norm_b(mixer(norm_a(x))), then x + norm_d(ff(norm_c(x))), on a float32 stream: every sublayer is normed on the way
+    in and on the way out.  Its norms are ``SandwichStreamRMSNorm``s named "mixer", "mixer_out", "feed_forward" and
+    "feed_forward_out"; what is handed on beside the stream is the last sublayer's output wrapped by its output norm, so
+    that ONE kernel norms it, adds it and norms the sum for the next sublayer.  A feed-forward with a bias on its last
+    product leaves that bias to the same kernel.  A layer may have no feed-forward."""
+
+    def pre_mixer(self, stream, pending):
+        return self.norms["mixer"].add_norm(stream, pending)
+
+    def post_mixer(self, stream, a, step):
+        pending = self.norms["mixer_out"].pending(a)
+        if self.feed_forward is not None:
+            h = self.norms["feed_forward"].add_norm(stream, pending)
+            if hasattr(self.feed_forward, "forward_deferred"):
+                f, bias = self.feed_forward.forward_deferred(h, step)
+            else:
+                f, bias = self.feed_forward.forward(h, step), None
+            pending = self.norms["feed_forward_out"].pending(f, bias)
+        rt = self.mixer.rt
+        if rt.trace is not None and self.prefix:
+            x = stream.clone()
+            self.norms["mixer_out"].settle(x, pending)
+            rt.record(f"{self.prefix}.out", x)
+        return stream, pending
+
+    def forward(self, stream, pending, step, cache, writes_cache=True):
+        h = self.pre_mixer(stream, pending)
+        a = self.mixer.forward(h, step, cache, writes_cache)
+        return self.post_mixer(stream, a, step)
+
+
 register_block("prenorm_residual", PreNormResidualBlock)
 register_block("prenorm_stream32", PreNormStreamBlock)
 register_block("outnorm_residual", OutputNormResidualBlock)
+register_block("sandwich_stream32", SandwichStreamBlock)

@@ -12,8 +12,8 @@ from typing import Dict, List, Optional
 
 import torch
 
-from . import (attention, block, embedding, feed_forward, latent_attention, mamba2, norm, position,  # noqa: F401  (register the parts)
-               routed_feed_forward, sink_attention)
+from . import (attention, block, embedding, feed_forward, latent_attention, mamba2, matrix_memory, norm,  # noqa: F401  (register the parts)
+               normed_attention, parallel, position, routed_feed_forward, sink_attention)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Runtime, StepState,
                    make)
 from .spec import ModelSpec, TensorSpec

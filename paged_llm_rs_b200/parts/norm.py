@@ -95,6 +95,61 @@ class ScaledStreamRMSNorm(RMSNorm):
         return out
 
 
+class PendingNormed:
+    """A sublayer's output that is still to be normed (by the norm that made this) and added to the stream: what a block
+    that norms its sublayers' outputs hands on, so that the next norm's kernel does all three."""
+
+    __slots__ = ("a", "gain", "bias", "eps")
+
+    def __init__(self, a, gain, bias, eps):
+        self.a, self.gain, self.bias, self.eps = a, gain, bias, eps
+
+
+class SandwichStreamRMSNorm(RMSNorm):
+    """RMSNorm in a decoder whose residual stream stays float32 and whose sublayers are normed on the way in AND on the way
+    out: x <- x + norm_out(sublayer(norm_in(x))).  As the norm on a sublayer's output it only wraps that output
+    (``pending``); as the norm on the next sublayer's input (or the model's last norm) ``add_norm`` takes the wrapped
+    output, norms it with ITS gain, adds it to the stream (in place) and norms the sum into the compute dtype, in one
+    kernel.  ``one_plus``: the file holds gain - 1."""
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.one_plus = bool(spec.params.get("one_plus", False))
+
+    def bind(self, tensors):
+        w = tensors[self._gain_name()]
+        self.gain = (w + 1.0) if self.one_plus else w
+
+    def pending(self, a, bias=None) -> PendingNormed:
+        return PendingNormed(a, self.gain, bias, self.eps)
+
+    def forward(self, x, rows=None):
+        return self.add_norm(x, None, rows)
+
+    def add_norm(self, residual, delta, rows=None):
+        if residual.dtype != torch.float32:
+            raise ValueError("the residual stream of this norm is float32")
+        if delta is not None and not isinstance(delta, PendingNormed):
+            raise ValueError("this norm adds a sublayer's output that another norm of its kind wrapped (pending)")
+        if delta is not None and delta.eps != self.eps:
+            raise ValueError("the norms of one stream share one eps")
+        n = rows.numel() if rows is not None else residual.shape[0]
+        out = torch.empty((n, self.width), dtype=self.rt.dtype, device=residual.device)
+        if delta is None:
+            ops.sandwich_norm32(residual, None, None, None, self.gain, out, self.eps, rows=rows)
+        else:
+            ops.sandwich_norm32(residual, delta.a, delta.bias, delta.gain, self.gain, out, self.eps, rows=rows)
+        self.rt.record(self._name("out"), out)
+        return out
+
+    @staticmethod
+    def settle(stream, delta: PendingNormed):
+        """stream += norm(delta), with no norm behind it."""
+        ops.sandwich_norm32(stream, delta.a, delta.bias, delta.gain, None, None, delta.eps)
+        return stream
+
+
 register_norm("rmsnorm", RMSNorm)
 register_norm("rmsnorm_stream32", StreamRMSNorm)
 register_norm("rmsnorm_scaled_stream32", ScaledStreamRMSNorm)
+register_norm("rmsnorm_sandwich_stream32", SandwichStreamRMSNorm)
