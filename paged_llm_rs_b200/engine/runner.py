@@ -237,6 +237,20 @@ class _DecodeGraph:
         return self.logits[:n], self.tokens[:1 + n]
 
 
+def group_plans(cache: CacheManager, mixer_of, page_size: int) -> List[Optional[GroupPlanConfig]]:
+    """Per cache group how its attention is cut into work items: what its mixers wish (those of one group alike; a group
+    whose mixers wish for nothing gets tables and slots only).  ``mixer_of(cell)`` gives the mixer a cache of the group
+    belongs to (``CacheGroup.cells``: a schedule entry, or (entry, part) for a part of a mixer made of several)."""
+    plans = []
+    for g in cache.groups:
+        wishes = {mixer_of(cell).plan_wish(page_size) for cell in g.cells}
+        if len(wishes) != 1:
+            raise ConfigError(f"the mixers that share a cache group wish for different attention plans: {sorted(map(str, wishes))}")
+        w = wishes.pop()
+        plans.append(None if w is None else GroupPlanConfig(w.tile_tokens, w.ctas_per_item, g.window, w.heads, w.head_dim))
+    return plans
+
+
 class ModelRunner:
     def __init__(self, model_dir: str, dtype="bfloat16", page_size: int = 16, num_pages: Optional[int] = None,
                  cache_bytes: Optional[int] = None, max_requests: int = 64, device: str = "cuda:0",
@@ -269,15 +283,7 @@ class ModelRunner:
         self.cache = CacheManager(needs, page_size, num_pages, max_requests, self.dtype, self.device,
                                   prefix_cache=prefix_cache)
         self.caches = self.cache.layer_caches()
-        # How each group's attention is cut into work items is what its mixers wish (those of one group alike);
-        # a group whose mixers wish for nothing gets tables and slots only.
-        plans = []
-        for g in self.cache.groups:
-            wishes = {self._mixer_of(cell).plan_wish(page_size) for cell in g.cells}
-            if len(wishes) != 1:
-                raise ConfigError(f"the mixers that share a cache group wish for different attention plans: {sorted(map(str, wishes))}")
-            w = wishes.pop()
-            plans.append(None if w is None else GroupPlanConfig(w.tile_tokens, w.ctas_per_item, g.window, w.heads, w.head_dim))
+        plans = group_plans(self.cache, self._mixer_of, page_size)
         # CTAs an attention launch should have before splits stop: one full wave at two CTAs an SM
         self.packer = StepPacker(self.cache, plans, 2 * ops.sm_count(), self.spec.vocab_size, self.spec.max_positions,
                                  self.device)
