@@ -755,6 +755,209 @@ def hybrid_kernels(z, pk):
     return out
 
 
+# ---- the matrix-memory decoder (Pamarax) beside the windowed-attention / state-space one (Bumisun) --------------------
+# Sizes that resemble real layers, at the widths of the 0.6B and of a 2B-class shape: attention of sixteen heads over
+# eight kv heads with keys of 128 entries that are also the values, half of each head rotated; a matrix LSTM of
+# width / 256 heads with keys of 128 and values of 256 entries; beside an attention with values of 64 entries, a gated
+# delta rule of width / 128 heads of 128 by 128 over half as many q/k heads, behind convolutions of four taps.  Layers
+# go attention, matrix LSTM, the two side by side, matrix LSTM; every layer has a dense gated feed-forward.  The other
+# model has the same width, layers, feed-forward and vocabulary: Mamba-2 layers and windowed attention in turn.
+MATRIX_SIZES = {
+    "1024": dict(width=1024, heads=16, kv_heads=8, dim=128, rot=64, left_vdim=64, temp_every=256, m_heads=4, m_dim=128, m_vdim=256,
+                 d_heads=8, d_kv_heads=4, d_dim=128, d_vdim=128, conv=4, ff=3072),
+    "2048": dict(width=2048, heads=16, kv_heads=8, dim=128, rot=64, left_vdim=64, temp_every=256, m_heads=8, m_dim=128, m_vdim=256,
+                 d_heads=16, d_kv_heads=8, d_dim=128, d_vdim=128, conv=4, ff=6144),
+}
+
+
+def matrix_config(z, layers):
+    att = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5,
+               rot=dict(dims=z["rot"], base=10000.0))
+    lstm = dict(heads=z["m_heads"], dim=z["m_dim"], vdim=z["m_vdim"], gate_cap=15.0)
+    left = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["left_vdim"], scale=z["dim"] ** -0.5,
+                q_temp=dict(coef=0.5, every=z["temp_every"]))
+    right = dict(heads=z["d_heads"], kv_heads=z["d_kv_heads"], dim=z["d_dim"], vdim=z["d_vdim"], conv=z["conv"])
+    cycle = [dict(type="attention", mixer=att), dict(type="mlstm", mixer=lstm),
+             dict(type="parallel", mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0)), dict(type="mlstm", mixer=lstm)]
+    return dict(architecture="Pamarax", vocab=LATENT_VOCAB, width=z["width"], norm=dict(eps=1e-6), embedding=dict(scale=1.0),
+                layers=[dict(cycle[i % 4], mlp=dict(kind="dense", ff=z["ff"])) for i in range(layers)])
+
+
+def matrix_beside_hybrid(size, layers, pk, clocks, steps, warmup, which="both"):
+    """Decode (batch 1, 8, 64 at context 4096) and the 2048-token prefill of the Pamarax shape ``size`` and of the Bumisun
+    shape of the same width, layers, dense feed-forward and vocabulary: tokens a second, side by side; then Pamarax's own
+    kernels alone beside the like kernels of Bumisun."""
+    import gc
+    import torch
+    from paged_llm_rs_b200 import Engine, write_random_model
+
+    z = MATRIX_SIZES[size]
+    hz = dict(HYBRID_SIZES[size], ff=z["ff"])
+    hybrid = hybrid_config(hz, layers)
+    for L in hybrid["layers"]:
+        L["mlp"] = dict(kind="dense", ff=z["ff"])
+    out = dict(size=size, layers=layers, vocab=LATENT_VOCAB, matrix=dict(z))
+    for name, cfg in (("pamarax", matrix_config(z, layers)), ("bumisun", hybrid)):
+        if which not in ("both", name):
+            continue
+        tmp = tempfile.mkdtemp(prefix="pllm_bench_", dir=scratch_dir())
+        try:
+            model_dir = write_random_model(os.path.join(tmp, "model"), cfg, 0, device="cuda")
+            ctx = 4096
+            pages = 64 * (ctx // PAGE + 4) + (PREFILL_TOKENS + 1024) // PAGE + 64
+            eng = Engine(model_dir, dtype="bfloat16", block_size=PAGE, blocks=pages, max_batch=64, chunk=PREFILL_TOKENS,
+                         prefix_cache=False)
+            shutil.rmtree(tmp, ignore_errors=True)
+            runner = eng.runner
+            for g in runner.cache.groups:
+                if g.pool is not None:
+                    g.pool.normal_(0.0, 1.0)
+            res = dict(weight_bytes=runner.weight_bytes(), cache_bytes_a_token=runner.cache.bytes_per_token())
+            for b in (1, 8, 64):
+                ms, launches, spread = decode_point(runner, b, ctx, max(5, steps // 2), warmup, clocks, repeats=4)
+                res[f"decode_b{b}_tok_s"] = round(b / (spread["median_ms"] / 1e3), 1)
+                res[f"decode_b{b}_ms"] = spread["median_ms"]
+                res[f"decode_b{b}_launches"] = launches
+            pms, _ = prefill_point(runner, LATENT_VOCAB, clocks, repeats=4)
+            res["prefill_ms"] = round(pms, 3)
+            res["prefill_tok_s"] = round(PREFILL_TOKENS / (pms / 1e3), 1)
+            out[name] = res
+            del eng, runner
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+            gc.collect()
+            torch.cuda.empty_cache()
+    out["kernels"] = matrix_kernels(z, pk)
+    like = hybrid_kernels(HYBRID_SIZES[size], pk)
+    out["kernels"].update({f"bumisun_{k}": v for k, v in like.items() if not k.startswith("qwen3_")})
+    return out
+
+
+def matrix_kernels(z, pk):
+    """Pamarax's own kernels alone, at the sizes of ``z``: device time (CUDA events, the median of nine after three
+    warm-ups, the cache pools and state slots larger than L2 where a model's would be), the algorithmic bytes and FLOPs,
+    and the fraction of the measured copy bandwidth or bfloat16 product rate they come to."""
+    import numpy as np
+    import torch
+    from paged_llm_rs_b200.kernels import attention_plan, ops
+    from paged_llm_rs_b200.parts.base import AttentionWork
+
+    dev, bf = "cuda", torch.bfloat16
+    nh, nkv, dk = z["heads"], z["kv_heads"], z["dim"]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    target = 2 * ops.sm_count()
+    out = {}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(9):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    def note(name, ms, nbytes, flops):
+        r = dict(us=round(ms * 1e3, 2), mbytes=round(nbytes / 1e6, 2), gflop=round(flops / 1e9, 3),
+                 hbm_frac=round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                 bf16_frac=round(flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4))
+        r["frac_of_slower_bound"] = round(max(r["hbm_frac"], r["bf16_frac"]), 4)
+        out[name] = r
+
+    def plan(segs, tile, ctas):
+        work, red, parts = attention_plan.plan_attention(segs, tile, 0, ctas, target)
+        wd = torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8).to(dev) if len(work) else torch.zeros(1, 8, dtype=torch.int32, device=dev)
+        rd = torch.from_numpy(np.ascontiguousarray(red)).reshape(-1, 4).to(dev) if len(red) else torch.zeros(1, 4, dtype=torch.int32, device=dev)
+        singles = all(n == 1 for _, n, _ in segs)
+        return lambda heads, hd: AttentionWork(wd, torch.tensor([len(work)], dtype=torch.int32, device=dev), max(len(work), 1), rd,
+                                                torch.tensor([len(red)], dtype=torch.int32, device=dev), len(red),
+                                                torch.zeros(max(parts, 1), heads, hd, device=dev), torch.zeros(max(parts, 1), heads, 2, device=dev),
+                                                kinds=1 if singles else 2, many_splits=attention_plan.many_splits(len(segs), ctas, target))
+
+    ctx, B, T = 4096, 64, PREFILL_TOKENS
+    n_pages = B * ctx // PAGE
+    tables = torch.randperm(n_pages, dtype=torch.int32).view(B, ctx // PAGE).to(dev)
+    cases = {"decode_b64_ctx4096": [(i, 1, ctx - 1) for i in range(B)], "prefill_2048": [(0, T, 0)]}
+    # -- attention over the whole context: keys that are the values (one more in no denominator), and the half beside the delta rule
+    for label, dv, sink in (("keys_are_values", dk, None), ("extra_one", z["left_vdim"], torch.zeros(nh, device=dev))):
+        pool = torch.randn(n_pages, nkv, PAGE, dk + dv, device=dev).to(bf)
+        for case, segs in cases.items():
+            n = sum(c for _, c, _ in segs)
+            keys = sum(p + i + 1 for _, c, p in segs for i in range(c))
+            q, o = torch.randn(n, nh * dk, device=dev).to(bf), torch.empty(n, nh * dv, dtype=bf, device=dev)
+            w = plan(segs, ops.attention_sink_tile_tokens(nh, nkv, bf, dk, dv), ops.attention_sink_ctas_per_item(nh, nkv, bf, dk, dv))(nh, dv)
+            ms = timed(lambda: ops.attention_sink(q, pool, tables, w, o, sink, nh, nkv, dk, dv, 0, 0, dk ** -0.5, 0.0, status))
+            seg_keys = sum(p + c for _, c, p in segs)
+            note(f"attention_{label}_{case}", ms, seg_keys * nkv * (dk + dv) * 2 + n * nh * (dk + dv) * 2, 2 * nh * (dk + dv) * keys)
+        del pool
+    # -- q/k norm, temperature, rotation and the cache write
+    pool = torch.randn(n_pages, nkv, PAGE, 2 * dk, device=dev).to(bf)
+    pool_l = torch.randn(n_pages, nkv, PAGE, dk + z["left_vdim"], device=dev).to(bf)
+    for case, n in (("decode_b64", B), ("prefill_2048", T)):
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        slots = torch.randperm(n_pages * PAGE, dtype=torch.int32)[:n].to(dev)
+        q = torch.empty(n, nh * dk, dtype=bf, device=dev)
+        inv = torch.rand(z["rot"] // 2, device=dev)
+        k_off, v_off = nh * dk, (nh + nkv) * dk
+        proj = torch.randn(n, (2 * nh + nkv) * dk, device=dev).to(bf)                  # q | k | gate
+        gq, gk = torch.ones(nh * dk, device=dev), torch.ones(nkv * dk, device=dev)
+        ms = timed(lambda: ops.normed_qk_kv_write(proj, k_off, v_off, q, gq, gk, "projection", 1e-6, 0.0, 0, inv, z["rot"], pos, slots, pool,
+                                                  nh, nkv, dk, dk, True, status))
+        note(f"normed_qk_kv_write_projection_{case}", ms, n * (nh + nkv) * dk * 2 + n * nh * dk * 2 + n * nkv * 2 * dk * 2, 0)
+        dv = z["left_vdim"]
+        proj2 = torch.randn(n, (nh + nkv) * dk + nkv * dv, device=dev).to(bf)
+        g1 = torch.ones(dk, device=dev)
+        ms = timed(lambda: ops.normed_qk_kv_write(proj2, k_off, v_off, q, g1, g1, "head", 1e-6, 0.5, z["temp_every"], None, 0, pos, slots, pool_l,
+                                                  nh, nkv, dk, dv, False, status))
+        note(f"normed_qk_kv_write_head_{case}", ms, 2 * proj2.numel() * 2, 0)
+    del pool, pool_l
+    # -- a sublayer's output normed and added, the next one's input normed: one pass over a float32 stream
+    W = z["width"]
+    for case, n in (("decode_b64", B), ("prefill_2048", T)):
+        x32, a = torch.randn(n, W, device=dev), torch.randn(n, W, device=dev).to(bf)
+        g1, y = torch.ones(W, device=dev), torch.empty(n, W, dtype=bf, device=dev)
+        ms = timed(lambda: ops.sandwich_norm32(x32, a, None, g1, g1, y, 1e-6))
+        note(f"sandwich_norm32_{case}", ms, n * W * (4 + 4 + 2 + 2), 0)
+    # -- the recurrent mixers between their projections
+    H, d, E = z["m_heads"], z["m_dim"], z["m_vdim"]
+    floats = ops.mlstm_state_floats(H, d, E)
+    state = torch.zeros(B + 1, floats, device=dev)
+    gain, hb = torch.ones(H * E, device=dev), torch.zeros(H, device=dev)
+    for case, segs in cases.items():
+        n = sum(c for _, c, _ in segs)
+        u = torch.randn(n, 2 * H * d + 2 * H * E, device=dev).to(bf)
+        gates = torch.randn(n, 2 * H, device=dev)
+        sg = torch.tensor([(t0, c, p, i + 1) for i, (t0, c, p) in enumerate(segs)], dtype=torch.int32, device=dev)
+        if len(segs) > 1:
+            sg[:, 0] = torch.arange(len(segs), dtype=torch.int32, device=dev)
+        y = torch.empty(n, H * E, dtype=bf, device=dev)
+        ms = timed(lambda: ops.mlstm_mix(u, gates, hb, hb, 15.0, gain, sg, state, y, H, d, E, 1e-6))
+        nbytes = u.numel() * 2 + gates.numel() * 4 + n * H * E * 4 * 2 + y.numel() * 2 + len(segs) * floats * 4 * 2
+        note(f"mlstm_mix_{case}", ms, nbytes, 6 * n * H * d * E)
+    del state
+    H, G, d, E, taps = z["d_heads"], z["d_kv_heads"], z["d_dim"], z["d_vdim"], z["conv"]
+    ch = 2 * G * d + H * E
+    floats = ops.delta_state_floats(H, G, d, E, taps)
+    state = torch.zeros(B + 1, floats, device=dev)
+    cw, gain, hb = torch.randn(ch, taps, device=dev).to(bf), torch.ones(E, device=dev), torch.zeros(H, device=dev)
+    for case, segs in cases.items():
+        n = sum(c for _, c, _ in segs)
+        u = torch.randn(n, ch + H * E, device=dev).to(bf)
+        ba = torch.randn(n, 2 * H, device=dev)
+        sg = torch.tensor([(t0, c, p, i + 1) for i, (t0, c, p) in enumerate(segs)], dtype=torch.int32, device=dev)
+        if len(segs) > 1:
+            sg[:, 0] = torch.arange(len(segs), dtype=torch.int32, device=dev)
+        y = torch.empty(n, H * E, dtype=bf, device=dev)
+        longest = max(c for _, c, _ in segs)
+        ms = timed(lambda: ops.delta_mix(u, cw, ba, hb, hb, gain, sg, longest, state, y, H, G, d, E, taps, 1e-6))
+        nbytes = u.numel() * 2 * 2 + n * ch * 4 * 2 + ba.numel() * 4 + n * H * E * 4 * 2 + y.numel() * 2 + len(segs) * floats * 4 * 2
+        note(f"delta_mix_{case}", ms, nbytes, 8 * n * H * d * E)
+    return out
+
+
 TRACE_KERNELS = {0: "(tcgen05 kernel)", 1: "embed", 2: "rmsnorm", 3: "swiglu", 4: "qk_norm_rope_kv", 5: "attention_generic", 6: "attention_reduce",
                  7: "attention_mma", 8: "attention_tma", 9: "skinny_gemm", 10: "sample_partial", 11: "sample_final", 12: "gemm_tcgen05", 13: "attention_tcgen05"}
 TRACE_FILES = ["elementwise", "qk_norm_rope_kv", "attention_generic", "attention_mma", "attention_decode_tma", "sampling",
@@ -912,7 +1115,11 @@ def main(argv=None) -> int:
     ap.add_argument("--hybrid-size", choices=sorted(HYBRID_SIZES), default="1024",
                     help="with --only hybrid: the width of the windowed-attention / state-space / clamped-experts decoder")
     ap.add_argument("--hybrid-model", choices=["both", "bumisun", "qwen3"], default="both", help="with --only hybrid: one model alone")
-    ap.add_argument("--only", choices=["decode", "prefill", "long-prompt", "timeline", "reference-kernel", "plain-cpu", "latent", "hybrid"], default=None,
+    ap.add_argument("--matrix-size", choices=sorted(MATRIX_SIZES), default="1024",
+                    help="with --only matrix: the width of the matrix-memory decoder (Pamarax)")
+    ap.add_argument("--matrix-model", choices=["both", "pamarax", "bumisun"], default="both", help="with --only matrix: one model alone")
+    ap.add_argument("--only", choices=["decode", "prefill", "long-prompt", "timeline", "reference-kernel", "plain-cpu", "latent", "hybrid", "matrix"],
+                    default=None,
                     help="run one part alone and print a short line (for profiling; not a bench record); "
                          "long-prompt: a prompt of --context tokens in portions of 2048, each portion timed; "
                          "timeline: one captured decode step as the kernels themselves clocked it; reference-kernel: "
@@ -921,7 +1128,9 @@ def main(argv=None) -> int:
                          "latent-attention / mixture-of-experts decoder (Surelorn) beside the Qwen3 shape of equal size "
                          "(--latent-size, --layers, default 8); hybrid: the same for the windowed-attention / state-space / "
                          "clamped-experts decoder (Bumisun), with its own kernels timed alone beside the like kernels of the "
-                         "Qwen3 shape (--hybrid-size, --layers, default 8)")
+                         "Qwen3 shape (--hybrid-size, --layers, default 8); matrix: decode and prefill of the matrix-memory decoder "
+                         "(Pamarax: gated attention, matrix LSTM, attention beside a gated delta rule) beside the Bumisun shape of "
+                         "equal size, with its own kernels timed alone beside Bumisun's like ones (--matrix-size, --layers, default 8)")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -957,6 +1166,12 @@ def main(argv=None) -> int:
     if args.only == "hybrid":
         clocks.start()
         out = hybrid_beside_dense(args.hybrid_size, args.layers or 8, pk, clocks, steps, warmup, which=args.hybrid_model)
+        out["clocks"] = clocks.stop()
+        print(json.dumps(out))
+        return 0
+    if args.only == "matrix":
+        clocks.start()
+        out = matrix_beside_hybrid(args.matrix_size, args.layers or 8, pk, clocks, steps, warmup, which=args.matrix_model)
         out["clocks"] = clocks.stop()
         print(json.dumps(out))
         return 0

@@ -1,6 +1,7 @@
 """A paged-KV inference engine for one B200: Qwen3 dense decoder, Surelorn
-(latent attention, routed experts) and Bumisun (windowed attention with sinks beside
-Mamba-2 layers, clamped experts), token ids in, token ids out.
+(latent attention, routed experts), Bumisun (windowed attention with sinks beside
+Mamba-2 layers, clamped experts) and Pamarax (gated attention with normed q/k, matrix
+LSTM layers, attention beside a gated delta rule), token ids in, token ids out.
 
     from paged_llm_rs_b200 import Engine
     engine = Engine("model_dir", dtype="bfloat16")
@@ -10,7 +11,7 @@ The CUDA kernels are compiled for sm_100a at the first call that needs them.
 """
 
 from . import models  # registers the architectures
-from .config import (Architecture, BumisunConfig, GenerationDefaults, Qwen3Config, SurelornConfig, load_config, register_architecture,
+from .config import (Architecture, BumisunConfig, GenerationDefaults, PamaraxConfig, Qwen3Config, SurelornConfig, load_config, register_architecture,
                      resolve_architecture)
 from .errors import (CacheError, ConfigError, EngineError, KernelError, UnsupportedModelError, WeightError)
 from .sampling import Rng, SamplingParams

@@ -3,3 +3,4 @@ from .registry import (Architecture, register_architecture, resolve_architecture
                        architecture_names)
 from .surelorn import SurelornConfig
 from .bumisun import BumisunConfig
+from .pamarax import PamaraxConfig

@@ -31,6 +31,7 @@ import os
 import sys
 
 PAGE_SIZE = 16
+MAX_REQUESTS = 4
 ROUND_TO = 64
 
 
@@ -42,6 +43,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE)
+    ap.add_argument("--max-requests", type=int, default=MAX_REQUESTS,
+                    help="requests that are live at any time: state slots and block tables are made for this many")
     ap.add_argument("--prefix-cache", choices=["on", "off"], default="off",
                     help="on: a request's first entry takes the pages that already hold its leading tokens "
                          "(never a page with a wanted place in it, never its last page) and runs the rest; "
@@ -67,7 +70,7 @@ def main(argv=None) -> int:
     graphs = args.graphs == "on"
     # Unless asked for, sharing of equal prefixes is off: a replayed request computes every token it is given.
     runner = ModelRunner(args.model, dtype=args.dtype, page_size=args.page_size, num_pages=pages,
-                         max_requests=8, prefix_cache=sharing, use_graphs=graphs)
+                         max_requests=args.max_requests, prefix_cache=sharing, use_graphs=graphs)
     if graphs and args.step_tokens:
         runner.graph_step_tokens = args.step_tokens
     cache = runner.cache
