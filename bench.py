@@ -934,7 +934,7 @@ def matrix_kernels(z, pk):
         if len(segs) > 1:
             sg[:, 0] = torch.arange(len(segs), dtype=torch.int32, device=dev)
         y = torch.empty(n, H * E, dtype=bf, device=dev)
-        ms = timed(lambda: ops.mlstm_mix(u, gates, hb, hb, 15.0, gain, sg, state, y, H, d, E, 1e-6))
+        ms = timed(lambda: ops.mlstm_mix(u, gates, hb, hb, 15.0, gain, sg, state, y, H, d, E, 1e-6, max(c for _, c, _ in segs)))
         nbytes = u.numel() * 2 + gates.numel() * 4 + n * H * E * 4 * 2 + y.numel() * 2 + len(segs) * floats * 4 * 2
         note(f"mlstm_mix_{case}", ms, nbytes, 6 * n * H * d * E)
     del state

@@ -104,7 +104,7 @@ def lib():
         sig["pllm_swiglu_bias"] = [c_int, P, P, P, c_int, c_int, c_int, c_float, P]
         sig["pllm_normed_qk_kv_write"] = [c_int, P, c_int, c_int, c_int, P, P, P, c_int, c_float, c_float, c_int, P, c_int, P, P, P] + [c_int] * 7 + [c_ll, P, P]
         sig["pllm_gate_mul"] = [c_int, P, P, c_int, c_int, c_int, c_int, P]
-        sig["pllm_mlstm_mix"] = [c_int, P, c_int, P, P, P, c_float, P, P, c_int, P, c_ll, P, P, P] + [c_int] * 4 + [c_float, P]
+        sig["pllm_mlstm_mix"] = [c_int, P, c_int, P, P, P, c_float, P, P, c_int, c_int, P, c_ll, P, P, P, P] + [c_int] * 4 + [c_float, P]
         sig["pllm_delta_mix"] = [c_int, P, c_int, P, P, P, P, P, P, c_int, c_int, P, c_ll, P, P, P] + [c_int] * 6 + [c_float, P]
         wide = {"pllm_mlstm_state_floats": [c_int] * 3, "pllm_delta_state_floats": [c_int] * 5}
         for name, args in wide.items():
@@ -1222,10 +1222,12 @@ def _segments_ok(segments: torch.Tensor, what: str):
 
 
 def mlstm_mix(u: torch.Tensor, gates: torch.Tensor, i_bias: torch.Tensor, f_bias: torch.Tensor, cap: float, gain: torch.Tensor,
-              segments: torch.Tensor, state: torch.Tensor, out: torch.Tensor, heads: int, dim: int, vdim: int, eps: float) -> torch.Tensor:
+              segments: torch.Tensor, state: torch.Tensor, out: torch.Tensor, heads: int, dim: int, vdim: int, eps: float,
+              max_segment_tokens: int = 0) -> torch.Tensor:
     """From the input projection's u [T, heads (2 dim + 2 vdim)] = [q | k | v | gate] and the gates' float32 projection
     [T, 2 heads] = [i | f] to the output projection's input [T, heads vdim]: the matrix memory's recurrence over each
-    segment's tokens from and into its state slot, each head over its root mean square, the gain, sigmoid(gate)."""
+    segment's tokens from and into its state slot, each head over its root mean square, the gain, sigmoid(gate).
+    max_segment_tokens bounds a segment's tokens where the caller knows it (a step of decoded tokens fetches fewer at a time)."""
     _dev(u, gates, i_bias, f_bias, gain, segments, state, out)
     for t, n in ((gates, "gates"), (i_bias, "i_bias"), (f_bias, "f_bias"), (gain, "gain"), (state, "state")):
         _f32(t, n)
@@ -1238,10 +1240,12 @@ def mlstm_mix(u: torch.Tensor, gates: torch.Tensor, i_bias: torch.Tensor, f_bias
     if state.dim() != 2 or state.shape[1] < mlstm_state_floats(heads, dim, vdim):
         raise KernelError("mlstm_mix: the state slots are too small")
     y_buf = torch.zeros((T, heads * vdim), dtype=torch.float32, device=u.device)     # (rows of no segment stay zero)
+    dn_buf = torch.zeros((T, heads, 2), dtype=torch.float32, device=u.device)
     nm_buf = torch.empty((segments.shape[0], heads, dim + 1), dtype=torch.float32, device=u.device)
     _check(lib().pllm_mlstm_mix(_code(u), _ptr(u), u.shape[1], _ptr(gates), _ptr(i_bias), _ptr(f_bias), float(cap), _ptr(gain),
-                                _ptr(segments), segments.shape[0], _ptr(state), state.stride(0), _ptr(nm_buf), _ptr(y_buf), _ptr(out), T,
-                                heads, dim, vdim, float(eps), _stream()), "mlstm_mix", launches=3)
+                                _ptr(segments), segments.shape[0], int(max_segment_tokens), _ptr(state), state.stride(0), _ptr(nm_buf),
+                                _ptr(dn_buf), _ptr(y_buf), _ptr(out), T, heads, dim, vdim, float(eps), _stream()),
+           "mlstm_mix", launches=3)
     return out
 
 

@@ -70,7 +70,7 @@ class MatrixLSTM(Mixer):
         gates = ops.linear(x, self.w_gates, out_dtype=torch.float32, status=st)
         y = torch.empty((x.shape[0], self.heads * self.vdim), dtype=x.dtype, device=x.device)
         ops.mlstm_mix(u, gates, self.i_bias, self.f_bias, self.cap, self.gain, step.segments, cache, y, self.heads, self.dim,
-                      self.vdim, self.eps)
+                      self.vdim, self.eps, max_segment_tokens=step.max_segment_tokens or 0)
         out = ops.linear(y, self.w_o, status=st)
         if self.rt.trace is not None:
             for leaf, t in (("in.out", u), ("gates", gates), ("o.in", y), ("out", out)):

@@ -469,13 +469,24 @@ def errors(got, want):
 TOL = {torch.float32: 2e-4, torch.bfloat16: 6e-2}
 
 
-def agrees(got, want, dtype):
-    """float32: every position within rounding.  bfloat16: the typical position well within and nine in ten not far: where a
+def rounding_alone(cfg, w, toks, want):
+    """Per position, the error of the plain implementation itself when it runs in float32: what rounding alone does there."""
+    P.F64 = torch.float32
+    try:
+        return errors(P.forward(cfg, w, toks).double(), want)
+    finally:
+        P.F64 = torch.float64
+
+
+def agrees(got, want, dtype, rounding=None):
+    """float32: every position within rounding (the fixed bound, or three times what rounding alone does at that position
+    where that is more).  bfloat16: the typical position well within and nine in ten not far: where a
     recurrent head's read-out nearly cancels (the first tokens above all, when the state holds one or two keys), its norm
     makes rounding decide the head's direction, and such a position differs by a large part of its logits."""
     e = errors(got, want)
     if dtype == torch.float32:
-        ok = float(e.max()) < TOL[dtype]
+        bound = torch.full_like(e, TOL[dtype]) if rounding is None else torch.clamp(3 * rounding.to(e), min=TOL[dtype])
+        ok = bool((e < bound).all())
     else:
         ok = float(e.median()) < TOL[dtype] and float(e.quantile(0.9)) < 0.3
     if not ok:
@@ -708,6 +719,7 @@ def test_configurations_drawn_at_random(tmp_path, seed):
     toks = tokens_for(cfg, 130, seed)
     folder, cfg, w = write_model(tmp_path, f"random{seed}", seed=seed, cfg=cfg)
     want = P.forward(cfg, w, toks)
+    rounding = rounding_alone(cfg, w, toks, want)
     for dtype in DTYPES:
         s = Served(folder, dtype, page=16, pages=24)
         whole = s.step([("w", toks, list(range(130)))])
@@ -717,5 +729,5 @@ def test_configurations_drawn_at_random(tmp_path, seed):
             outs.append(s.step([("c", toks[at:at + c], list(range(c)))]))
             at += c
         assert at == 130
-        assert agrees(whole, want, dtype), (seed, dtype, cfg)
-        assert agrees(torch.cat(outs), want, dtype), (seed, dtype, cfg)
+        assert agrees(whole, want, dtype, rounding), (seed, dtype, cfg)
+        assert agrees(torch.cat(outs), want, dtype, rounding), (seed, dtype, cfg)
