@@ -854,6 +854,7 @@ def matrix_kernels(z, pk):
         torch.cuda.synchronize()
         ts = []
         for _ in range(9):
+            flush_l2()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(); fn(); b.record()
             torch.cuda.synchronize()

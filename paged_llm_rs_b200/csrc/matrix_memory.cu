@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(256, MINB) delta_scan_kernel(const float* __re
 // and head to dn; the division waits for the kernel behind this one.  The last MM_FETCHERS threads fetch the NEXT chunk
 // meanwhile (two buffers) and turn its gates into the three factors of a token, the running maximum going from token to token.
 // u: [tokens, u_width] of the compute dtype, q at 0 (H d), k at H d, v at 2 H d (H e).  gates: [tokens, 2 H] float, i_raw | f_raw.
-#define MM_FETCHERS 128
+#define MM_FETCHERS (32 + MM_LOADERS)      // a warp for the gates, the others for keys, queries and values
 #define MM_SCAN_THREADS (256 + 32 + MM_FETCHERS)
 template <typename T, int NPT>
 __global__ void __launch_bounds__(MM_SCAN_THREADS, 1) mlstm_scan_kernel(const T* __restrict__ u, int u_width, const float* __restrict__ gates,
@@ -393,30 +393,27 @@ __global__ void __launch_bounds__(MM_SCAN_THREADS, 1) mlstm_scan_kernel(const T*
                 float* k_s = q_s + ck * NP;
                 float* v_s = k_s + ck * NP;
                 float* a_s = v_s + ck * Ps;
-                // every load of the chunk leaves before the first one is waited for: the gates, the values' first rounds,
-                // then keys and queries
-                float rf = 0.f, ri = 0.f;
-                if (ft < nt) {
-                    const float* r = gates + (size_t)(s.first + t0 + ft) * 2 * H;
-                    rf = r[H + h]; ri = r[h];
-                }
+                // every load of the chunk leaves before the first one is waited for: the values' first rounds, then keys
+                // and queries
+                if (ft >= 32) {
+                const int fl = ft - 32;
                 float rv[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const int i = ft + j * MM_FETCHERS, ee = p0 + i % Ps;
+                    const int i = fl + j * MM_LOADERS, ee = p0 + i % Ps;
                     rv[j] = (i < nt * Ps && ee < E) ? to_f32(u[(size_t)(s.first + t0 + i / Ps) * u_width + 2 * H * d + h * E + ee]) : 0.f;
                 }
                 if (vec) {
                     const int dv = d / VEC;
 #pragma unroll 4
-                    for (int i = ft; i < nt * dv; i += MM_FETCHERS) {
+                    for (int i = fl; i < nt * dv; i += MM_LOADERS) {
                         const int t = i / dv, j = (i - t * dv) * VEC;
                         const T* row = u + (size_t)(s.first + t0 + t) * u_width + h * d + j;
                         mm_fetch16(row, q_s + t * NP + j, q_scale);
                         mm_fetch16(row + (size_t)H * d, k_s + t * NP + j, 1.f);
                     }
                 } else {
-                    for (int i = ft; i < nt * d; i += MM_FETCHERS) {
+                    for (int i = fl; i < nt * d; i += MM_LOADERS) {
                         const T* row = u + (size_t)(s.first + t0 + i / d) * u_width + h * d + i % d;
                         q_s[(i / d) * NP + i % d] = to_f32(row[0]) * q_scale;
                         k_s[(i / d) * NP + i % d] = to_f32(row[(size_t)H * d]);
@@ -424,20 +421,22 @@ __global__ void __launch_bounds__(MM_SCAN_THREADS, 1) mlstm_scan_kernel(const T*
                 }
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const int i = ft + j * MM_FETCHERS;
+                    const int i = fl + j * MM_LOADERS;
                     if (i < nt * Ps) v_s[i] = rv[j];
                 }
 #pragma unroll 4
-                for (int i = ft + 4 * MM_FETCHERS; i < nt * Ps; i += MM_FETCHERS) {
+                for (int i = fl + 4 * MM_LOADERS; i < nt * Ps; i += MM_LOADERS) {
                     const int ee = p0 + i % Ps;
                     v_s[i] = ee < E ? to_f32(u[(size_t)(s.first + t0 + i / Ps) * u_width + 2 * H * d + h * E + ee]) : 0.f;
                 }
-                if (ft < 32) {
-                    // lane t has token t's gates; the running maximum goes from token to token, every lane following it
+                } else {
+                    // the fetchers' first warp: lane t has token t's gates; the running maximum goes from token to token,
+                    // every lane following it
                     float fg = 0.f, ig = 0.f;
                     if (lane < nt) {
-                        fg = mm_logsigmoid(cap * tanhf((rf + bf) / cap));
-                        ig = cap * tanhf((ri + bi) / cap);
+                        const float* r = gates + (size_t)(s.first + t0 + lane) * 2 * H;
+                        fg = mm_logsigmoid(cap * tanhf((r[H + h] + bf) / cap));
+                        ig = cap * tanhf((r[h] + bi) / cap);
                     }
                     float m_old = 0.f, m_new = 0.f;
                     for (int t = 0; t < nt; t++) {
