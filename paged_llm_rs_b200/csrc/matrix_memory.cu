@@ -15,9 +15,12 @@
 //
 // A step is a list of segments {first token, tokens, tokens before, state slot} on the device; grids are sized by the list's
 // capacity and a segment of no tokens does nothing, so a captured step replays for any step that fits.
-// A thread holds rows part, part + PARTS, ... of ONE column of S; the PARTS threads of a column are neighbours in a warp and
-// meet by shuffles in a fixed order, columns never meet: what a token's output is does not depend on how the columns are
-// shared out among CTAs, nor on where a prompt was cut.  Other threads of the CTA fetch the tokens ahead of the recurrence.
+// A thread holds some rows of ONE column of S in registers.  Delta rule: rows part, part + PARTS, ...; the PARTS threads of a
+// column are neighbours in a warp and meet by shuffles in a fixed order before every write.  Matrix LSTM: rows part NPT ...;
+// a column's threads never meet, their shares of a read-out are added in the order of the parts once a chunk.  Columns never
+// meet: what a token's output is does not depend on how the columns are shared out among CTAs, and on where a prompt was
+// cut only by the rounding of the delta rule's pairs of tokens.  Other threads of the CTA fetch the tokens ahead of the
+// recurrence.
 #include "common.cuh"
 
 enum : int { KID_MATRIX_MEMORY = 100 };
