@@ -731,3 +731,41 @@ def test_configurations_drawn_at_random(tmp_path, seed):
         assert at == 130
         assert agrees(whole, want, dtype, rounding), (seed, dtype, cfg)
         assert agrees(torch.cat(outs), want, dtype, rounding), (seed, dtype, cfg)
+
+
+FAR_SIZES = {
+    # keys of 256 and 512 entries, a value of 4, a delta rule without convolution (one tap), six heads over two q/k heads
+    "long_keys": lambda: model(300, 256, [
+        layer(mlstm(2, 256, 128, cap=10.0), dense(64)),
+        layer(parallel(left(4, 2, 128, 96, coef=0.7, every=5, scale=0.1), right(6, 2, 256, 64, conv=1), 0.9, 1.1), None),
+        layer(attention(6, 3, 96, rot=32, base=1000.0, scale=0.2), dense(96)),
+        layer(mlstm(1, 512, 4, cap=3.0), None)], eps=1e-6, embedding_scale=2.0),
+    # keys of 4 entries beside values of 200 and 300, sixteen taps, sizes that are no multiple of eight
+    "short_keys": lambda: model(130, 72, [
+        layer(parallel(left(3, 1, 40, 4, coef=0.2, every=2, scale=0.3), right(2, 1, 4, 200, conv=7), 1.0, 0.5), dense(40)),
+        layer(mlstm(5, 4, 300, cap=20.0), dense(24)),
+        layer(mlstm(3, 36, 20, cap=1.0), None),
+        layer(parallel(left(2, 2, 8, 8, coef=0.0, every=0, scale=0.5), right(3, 3, 100, 36, conv=16), 0.3, 2.0), None)],
+        eps=1e-5, embedding_scale=1.0),
+}
+
+
+@pytest.mark.parametrize("name", sorted(FAR_SIZES))
+def test_sizes_far_from_the_usual(tmp_path, name):
+    """State matrices much longer than wide and much wider than long, whole and in portions with decoded tokens behind."""
+    cfg = FAR_SIZES[name]()
+    toks = tokens_for(cfg, 150, 5)
+    folder, cfg, w = write_model(tmp_path, name, seed=7, cfg=cfg)
+    want = P.forward(cfg, w, toks)
+    rounding = rounding_alone(cfg, w, toks, want)
+    for dtype in DTYPES:
+        s = Served(folder, dtype, page=16, pages=40)
+        whole = s.step([("w", toks, list(range(150)))])
+        s.end("w")
+        outs, at = [], 0
+        for c in [37, 2, 64, 33] + [1] * 14:
+            outs.append(s.step([("c", toks[at:at + c], list(range(c)))]))
+            at += c
+        assert at == 150
+        assert agrees(whole, want, dtype, rounding), (name, dtype)
+        assert agrees(torch.cat(outs), want, dtype, rounding), (name, dtype)
