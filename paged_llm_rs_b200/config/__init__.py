@@ -4,3 +4,4 @@ from .registry import (Architecture, register_architecture, resolve_architecture
 from .surelorn import SurelornConfig
 from .bumisun import BumisunConfig
 from .pamarax import PamaraxConfig
+from .tebozen import TebozenConfig

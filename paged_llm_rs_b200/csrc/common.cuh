@@ -47,6 +47,15 @@ __device__ __forceinline__ float glu_act(int kind, float limit, float g, float u
     return g / (1.0f + expf(-g)) * u;
 }
 
+// The one-argument activations y = act(u) of feed-forwards without a gate:
+//   UNARY_NONE   u
+//   UNARY_RELU2  max(u, 0)^2
+enum : int { UNARY_NONE = 0, UNARY_RELU2 = 1 };
+__device__ __forceinline__ float unary_act(int kind, float u) {
+    if (kind == UNARY_RELU2) { u = fmaxf(u, 0.f); return u * u; }
+    return u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

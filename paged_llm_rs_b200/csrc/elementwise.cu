@@ -365,6 +365,25 @@ PLLM_EXPORT int pllm_swiglu(int dtype, const void* in, void* out, int n_rows, in
     return launch_status();
 }
 
+// A one-argument activation in place (a feed-forward without a gate): x = act(x).
+template <typename T>
+__global__ void unary_act_kernel(T* x, long long total, int act) {
+    pdl_launch_dependents();
+    pdl_wait(KID_SWIGLU);
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x)
+        x[idx] = from_f32<T>(unary_act(act, to_f32(x[idx])));
+}
+
+PLLM_EXPORT int pllm_unary_act(int dtype, void* x, long long total, int act, cudaStream_t stream) {
+    if (total <= 0) return PLLM_OK;
+    if (act < UNARY_NONE || act > UNARY_RELU2) return PLLM_ERR_SIZE;
+    PLLM_DISPATCH_DTYPE(dtype, {
+        int blocks = (int)min((long long)sm_count() * 16, (total + 255) / 256);
+        launch_chained(unary_act_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)x, total, act);
+    });
+    return launch_status();
+}
+
 // The same with a bias on each half first: out = act(g + bias[c], u + bias[inter + c]); bias float [2 inter].
 template <typename T>
 __global__ void swiglu_bias_kernel(const T* in, const float* __restrict__ bias, T* __restrict__ out, int inter, long long total, int act,

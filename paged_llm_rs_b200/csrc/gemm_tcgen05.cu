@@ -188,8 +188,16 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tcgen05_kernel(const __grid
                     }
                 } else {
                     tmem_wait_ld();
+                    if (act == UNARY_NONE) {
 #pragma unroll
-                    for (int k = 0; k < 16; k++) out[k] = pack2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
+                        for (int k = 0; k < 16; k++) out[k] = pack2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
+                    } else {
+                        // a one-argument activation of the product, rounded first as a product of its own would leave it
+#pragma unroll
+                        for (int k = 0; k < 16; k++)
+                            out[k] = pack2(unary_act(act, round_bf16(__uint_as_float(v[2 * k]))),
+                                           unary_act(act, round_bf16(__uint_as_float(v[2 * k + 1]))));
+                    }
                 }
                 if (c == OUT_BN / 32 - 1) {
                     // everything of this accumulator is in registers: the tensor cores may have it back
@@ -253,11 +261,14 @@ int launch_gemm(const void* x, const void* w, void* y, int M, int n_out, int K, 
 }  // namespace
 
 // x: [M, K]; w: [n_out, K], or with glu [2 n_out, K] = gate rows then up rows; y: [M, n_out]; all bfloat16.
-// glu: 0 a plain product, else 1 + the gated activation's kind (common.cuh), with its limit.
+// glu: 0 a plain product; positive: 1 + the gated activation's kind (common.cuh), with its limit; negative: minus a one-argument
+// activation's kind (UNARY_*), applied to the plain product.
 PLLM_EXPORT int pllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, int n_out, int K, int glu, float limit, int* status,
                                   cudaStream_t stream) {
-    if (!pllm_gemm_tcgen05_supports(M, n_out, K, glu) || glu < 0 || glu > 1 + GLU_CLAMPED) return PLLM_ERR_SIZE;
-    const int act = glu ? glu - 1 : GLU_SILU;
+    const int unary = glu < 0 ? -glu : UNARY_NONE;
+    if (glu < 0) glu = 0;
+    if (!pllm_gemm_tcgen05_supports(M, n_out, K, glu) || unary > UNARY_RELU2 || glu > 1 + GLU_CLAMPED) return PLLM_ERR_SIZE;
+    const int act = glu ? glu - 1 : unary;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return PLLM_ERR_ALIGN;
     // tiles of 256 columns of W where the width divides into them and they still give every SM one
     const int tiles_m = (M + G_BM - 1) / G_BM;
@@ -266,17 +277,19 @@ PLLM_EXPORT int pllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, 
     if (glu)
         return wide ? launch_gemm<1, 256>(x, w, y, M, n_out, K, status, stream, nullptr, 1, act, limit)
                     : launch_gemm<1, 128>(x, w, y, M, n_out, K, status, stream, nullptr, 1, act, limit);
-    return wide ? launch_gemm<0, 256>(x, w, y, M, n_out, K, status, stream)
-                : launch_gemm<0, 128>(x, w, y, M, n_out, K, status, stream);
+    return wide ? launch_gemm<0, 256>(x, w, y, M, n_out, K, status, stream, nullptr, 1, act)
+                : launch_gemm<0, 128>(x, w, y, M, n_out, K, status, stream, nullptr, 1, act);
 }
 
 // The grouped form: x [M, K] holds the rows sorted by expert, each expert's rows padded to whole tiles of 128
 // (M a multiple of 128, an upper bound); w [experts, n_out (glu: 2 n_out), K]; tile_expert [M / 128] on the device.
 PLLM_EXPORT int pllm_gemm_tcgen05_grouped(const void* x, const void* w, void* y, int M, int n_out, int K, int glu, float limit,
                                           const int* tile_expert, int n_experts, int* status, cudaStream_t stream) {
+    const int unary = glu < 0 ? -glu : UNARY_NONE;
+    if (glu < 0) glu = 0;
     if (!pllm_gemm_tcgen05_supports(M, n_out, K, glu) || M % G_BM || n_experts < 1 || !tile_expert) return PLLM_ERR_SIZE;
-    if (glu < 0 || glu > 1 + GLU_CLAMPED) return PLLM_ERR_SIZE;
-    const int act = glu ? glu - 1 : GLU_SILU;
+    if (unary > UNARY_RELU2 || glu > 1 + GLU_CLAMPED) return PLLM_ERR_SIZE;
+    const int act = glu ? glu - 1 : unary;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return PLLM_ERR_ALIGN;
     const int tiles_m = M / G_BM;
     const int unit = glu ? 128 : 256;
@@ -284,8 +297,8 @@ PLLM_EXPORT int pllm_gemm_tcgen05_grouped(const void* x, const void* w, void* y,
     if (glu)
         return wide ? launch_gemm<1, 256>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts, act, limit)
                     : launch_gemm<1, 128>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts, act, limit);
-    return wide ? launch_gemm<0, 256>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts)
-                : launch_gemm<0, 128>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts);
+    return wide ? launch_gemm<0, 256>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts, act)
+                : launch_gemm<0, 128>(x, w, y, M, n_out, K, status, stream, tile_expert, n_experts, act);
 }
 
 PLLM_TRACE_EXPORT(gemm_tcgen05)

@@ -24,6 +24,9 @@ enum : int { KID_MOE = 60 };
 
 #define MOE_MAX_OUTPUTS 1024
 #define MOE_MAX_TOP 32
+// how router logits become scores and weights (bits of `scoring`): a sigmoid of each logit instead of the softmax over
+// all; the chosen scores themselves as weights instead of their shares of the chosen scores' sum
+enum : int { MOE_SCORE_SIGMOID = 1, MOE_SCORE_RAW_WEIGHTS = 2 };
 
 // Every lane brings its best (value, index); all leave with the warp's best, ties to the lower index.
 __device__ __forceinline__ void warp_argmax(float& best, int& at) {
@@ -44,7 +47,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float*
                                                         const float* __restrict__ correction, int* __restrict__ ids,
                                                         float* __restrict__ weights, int n_tokens, int width, int outputs,
                                                         int top, int groups, int keep, const float* __restrict__ bias, int extra,
-                                                        float* __restrict__ extra_out) {
+                                                        float* __restrict__ extra_out, int scoring) {
     extern __shared__ float smem[];      // xs[TOK][width]; per token: s[outputs], choice[outputs], gscore[groups]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t0 = blockIdx.x * TOK;
@@ -109,17 +112,25 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float*
         float* choice = s + outputs;
         float* gscore = choice + outputs;
         if (lane < extra) extra_out[(size_t)t * extra + lane] = gscore[groups + lane];
-        float zmax = -CUDART_INF_F;
-        for (int e = lane; e < outputs; e += 32) zmax = fmaxf(zmax, s[e]);
-        zmax = warp_max(zmax);
-        float sum = 0.f;
-        for (int e = lane; e < outputs; e += 32) { const float p = expf(s[e] - zmax); s[e] = p; sum += p; }
-        sum = warp_sum(sum);
-        __syncwarp();
-        for (int e = lane; e < outputs; e += 32) {
-            const float p = s[e] / sum;
-            s[e] = p;
-            choice[e] = p + (correction ? correction[e] : 0.f);
+        if (scoring & MOE_SCORE_SIGMOID) {
+            for (int e = lane; e < outputs; e += 32) {
+                const float p = 1.0f / (1.0f + expf(-s[e]));
+                s[e] = p;
+                choice[e] = p + (correction ? correction[e] : 0.f);
+            }
+        } else {
+            float zmax = -CUDART_INF_F;
+            for (int e = lane; e < outputs; e += 32) zmax = fmaxf(zmax, s[e]);
+            zmax = warp_max(zmax);
+            float sum = 0.f;
+            for (int e = lane; e < outputs; e += 32) { const float p = expf(s[e] - zmax); s[e] = p; sum += p; }
+            sum = warp_sum(sum);
+            __syncwarp();
+            for (int e = lane; e < outputs; e += 32) {
+                const float p = s[e] / sum;
+                s[e] = p;
+                choice[e] = p + (correction ? correction[e] : 0.f);
+            }
         }
         __syncwarp();
         // groups: keep the best `keep`, the others' outputs cannot be chosen
@@ -166,7 +177,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float*
         }
         if (lane < top) {
             ids[(size_t)t * top + lane] = mine_id;
-            weights[(size_t)t * top + lane] = mine_s / (wsum + 1e-20f);
+            weights[(size_t)t * top + lane] = (scoring & MOE_SCORE_RAW_WEIGHTS) ? mine_s : mine_s / (wsum + 1e-20f);
         }
     }
 }
@@ -174,18 +185,19 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* h, const float*
 template <typename T, int TOK>
 static void launch_route(const void* h, const float* w_router, const float* correction, int* ids, float* weights, int n_tokens,
                          int width, int outputs, int top, int groups, int keep, const float* bias, int extra, float* extra_out,
-                         cudaStream_t stream) {
+                         int scoring, cudaStream_t stream) {
     const size_t smem = ((size_t)TOK * width + (size_t)TOK * (2 * outputs + groups + extra)) * sizeof(float);
     cudaFuncSetAttribute(moe_route_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_chained(moe_route_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, stream, (const T*)h, w_router,
-                   correction, ids, weights, n_tokens, width, outputs, top, groups, keep, bias, extra, extra_out);
+                   correction, ids, weights, n_tokens, width, outputs, top, groups, keep, bias, extra, extra_out, scoring);
 }
 
 // bias: [outputs] or null.  extra (<= 32): rows of w_router behind the outputs; extra_out [tokens, extra] receives their products.
 PLLM_EXPORT int pllm_moe_route(int dtype, const void* h, const float* w_router, const float* correction, int* ids, float* weights,
                                int n_tokens, int width, int outputs, int top, int groups, int keep, const float* bias, int extra,
-                               float* extra_out, cudaStream_t stream) {
+                               float* extra_out, int scoring, cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
+    if (scoring < 0 || scoring > 3) return PLLM_ERR_SIZE;
     if (extra < 0 || extra > 32 || (extra > 0 && !extra_out)) return PLLM_ERR_SIZE;
     if (width <= 0 || outputs <= 0 || top <= 0 || groups <= 0 || keep <= 0 || outputs % groups || keep > groups) return PLLM_ERR_SIZE;
     if (outputs > MOE_MAX_OUTPUTS || top > MOE_MAX_TOP || top > outputs) return PLLM_ERR_LIMIT;
@@ -193,8 +205,8 @@ PLLM_EXPORT int pllm_moe_route(int dtype, const void* h, const float* w_router, 
     const bool many = n_tokens >= 256 && (8 * (size_t)width + 8 * (size_t)(2 * outputs + groups + extra)) * sizeof(float) <= 160 * 1024;
     if (((size_t)width + 2 * outputs + groups + extra) * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
     PLLM_DISPATCH_DTYPE(dtype, {
-        if (many) launch_route<T, 8>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, bias, extra, extra_out, stream);
-        else launch_route<T, 1>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, bias, extra, extra_out, stream);
+        if (many) launch_route<T, 8>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, bias, extra, extra_out, scoring, stream);
+        else launch_route<T, 1>(h, w_router, correction, ids, weights, n_tokens, width, outputs, top, groups, keep, bias, extra, extra_out, scoring, stream);
     });
     return launch_status();
 }
@@ -204,9 +216,13 @@ PLLM_EXPORT int pllm_moe_route(int dtype, const void* h, const float* w_router, 
 // grid (pairs, column blocks); a CTA keeps the token's row in shared memory as floats; a warp forms PAIR_CW columns
 // at a time, so that the loads of 2 * PAIR_CW weight rows are in flight together.
 #define PAIR_CW 4
-template <typename T>
+// GATED false: the experts have no gate rows (w_gu is [experts, ff, width]) and `glu` names a one-argument activation
+// (common.cuh: UNARY_*).  in_weights [pairs] or null: the expert reads the token times the pair's weight, which is the weight
+// times the products with the token itself.
+template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int* ids, const T* __restrict__ w_gu, T* __restrict__ act,
-                                                           int width, int ff, int top, int experts, int glu, float limit) {
+                                                           int width, int ff, int top, int experts, int glu, float limit,
+                                                           const float* __restrict__ in_weights) {
     extern __shared__ float xs[];
     const int pair = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_launch_dependents();
@@ -222,8 +238,9 @@ __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int
         for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32(hr[c]);
     }
     __syncthreads();
-    const T* wg = w_gu + (size_t)e * 2 * ff * width;
-    const T* wu = wg + (size_t)ff * width;
+    const T* wg = w_gu + (size_t)e * (GATED ? 2 : 1) * ff * width;
+    const T* wu = GATED ? wg + (size_t)ff * width : wg;
+    const float in_w = in_weights ? in_weights[pair] : 1.0f;
     const int col0 = (blockIdx.y * 8 + warp) * PAIR_CW;
     if (col0 >= ff) return;
     float ag[PAIR_CW], au[PAIR_CW];
@@ -236,13 +253,19 @@ __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int
 #pragma unroll
             for (int j = 0; j < PAIR_CW; j++) {
                 const int col = min(col0 + j, ff - 1);           // (a column past the end repeats the last one and is not stored)
-                vg[j].load(wg + (size_t)col * width + c); vu[j].load(wu + (size_t)col * width + c);
+                if (GATED) vg[j].load(wg + (size_t)col * width + c);
+                vu[j].load(wu + (size_t)col * width + c);
             }
 #pragma unroll
             for (int j = 0; j < PAIR_CW; j++) {
-                float fg[N], fu[N]; vg[j].unpack(fg); vu[j].unpack(fu);
+                float fg[N], fu[N];
+                if (GATED) vg[j].unpack(fg);
+                vu[j].unpack(fu);
 #pragma unroll
-                for (int k = 0; k < N; k++) { ag[j] = fmaf(xs[c + k], fg[k], ag[j]); au[j] = fmaf(xs[c + k], fu[k], au[j]); }
+                for (int k = 0; k < N; k++) {
+                    if (GATED) ag[j] = fmaf(xs[c + k], fg[k], ag[j]);
+                    au[j] = fmaf(xs[c + k], fu[k], au[j]);
+                }
             }
         }
     } else {
@@ -250,15 +273,16 @@ __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int
 #pragma unroll
             for (int j = 0; j < PAIR_CW; j++) {
                 const int col = min(col0 + j, ff - 1);
-                ag[j] = fmaf(xs[c], to_f32(wg[(size_t)col * width + c]), ag[j]);
+                if (GATED) ag[j] = fmaf(xs[c], to_f32(wg[(size_t)col * width + c]), ag[j]);
                 au[j] = fmaf(xs[c], to_f32(wu[(size_t)col * width + c]), au[j]);
             }
         }
     }
 #pragma unroll
     for (int j = 0; j < PAIR_CW; j++) {
-        const float g = warp_sum(ag[j]), u = warp_sum(au[j]);
-        if (lane == 0 && col0 + j < ff) act[(size_t)pair * ff + col0 + j] = from_f32<T>(glu_act(glu, limit, g, u));
+        const float g = GATED ? warp_sum(ag[j]) * in_w : 0.f, u = warp_sum(au[j]) * in_w;
+        if (lane == 0 && col0 + j < ff)
+            act[(size_t)pair * ff + col0 + j] = from_f32<T>(GATED ? glu_act(glu, limit, g, u) : unary_act(glu, u));
     }
 }
 
@@ -268,7 +292,8 @@ __global__ void __launch_bounds__(256) moe_pair_glu_kernel(const T* h, const int
 template <typename T, int CW>
 __global__ void __launch_bounds__(256) moe_pair_down_kernel(const T* act, const T* h, const int* ids, const float* weights,
                                                             const T* __restrict__ w_d, const T* shared, T* __restrict__ out,
-                                                            int width, int ff, int top, int experts, const float* shared_gate) {
+                                                            int width, int ff, int top, int experts, const float* shared_gate,
+                                                            int unit_weights) {
     extern __shared__ float xs[];                 // [top][ff]: weight_k * activation of expert k (zeros for an identity expert)
     __shared__ int id_s[MOE_MAX_TOP];
     __shared__ float idw_s;                       // the identity experts' weights, summed
@@ -277,7 +302,7 @@ __global__ void __launch_bounds__(256) moe_pair_down_kernel(const T* act, const 
     pdl_wait(KID_MOE);
     if (threadIdx.x < 32) {
         int e = -1; float w = 0.f;
-        if (lane < top) { e = ids[(size_t)t * top + lane]; w = weights[(size_t)t * top + lane]; }
+        if (lane < top) { e = ids[(size_t)t * top + lane]; w = weights[(size_t)t * top + lane]; }     // (an identity expert's weight counts either way)
         const bool identity = lane < top && (e < 0 || e >= experts);
         if (lane < top) id_s[lane] = identity ? -1 : e;
         const float iw = warp_sum(identity ? w : 0.f);
@@ -286,7 +311,7 @@ __global__ void __launch_bounds__(256) moe_pair_down_kernel(const T* act, const 
     __syncthreads();
     for (int i = threadIdx.x; i < top * ff; i += blockDim.x) {
         const int k = i / ff;
-        xs[i] = id_s[k] < 0 ? 0.f : weights[(size_t)t * top + k] * to_f32(act[((size_t)t * top + k) * ff + i % ff]);
+        xs[i] = id_s[k] < 0 ? 0.f : (unit_weights ? 1.0f : weights[(size_t)t * top + k]) * to_f32(act[((size_t)t * top + k) * ff + i % ff]);
     }
     __syncthreads();
     constexpr int N = Vec16<T>::N;
@@ -336,23 +361,33 @@ __global__ void __launch_bounds__(256) moe_pair_down_kernel(const T* act, const 
     }
 }
 
+// glu: a gated activation's kind (GLU_*), or with gated 0 a one-argument activation's (UNARY_*) for experts without gate rows.
 PLLM_EXPORT int pllm_moe_pair_glu(int dtype, const void* h, const int* ids, const void* w_gu, void* act, int n_tokens, int width,
-                                  int ff, int top, int experts, int glu, float limit, cudaStream_t stream) {
+                                  int ff, int top, int experts, int glu, float limit, int gated, const float* in_weights,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
-    if (glu < GLU_SILU || glu > GLU_CLAMPED) return PLLM_ERR_SIZE;
+    if (gated ? (glu < GLU_SILU || glu > GLU_CLAMPED) : (glu < UNARY_NONE || glu > UNARY_RELU2)) return PLLM_ERR_SIZE;
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
     if ((size_t)width * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
+    const dim3 grid(n_tokens * top, (ff + 8 * PAIR_CW - 1) / (8 * PAIR_CW));
+    const size_t smem = (size_t)width * sizeof(float);
     PLLM_DISPATCH_DTYPE(dtype, {
-        cudaFuncSetAttribute(moe_pair_glu_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)width * sizeof(float)));
-        launch_chained(moe_pair_glu_kernel<T>, dim3(n_tokens * top, (ff + 8 * PAIR_CW - 1) / (8 * PAIR_CW)), dim3(256),
-                       (size_t)width * sizeof(float), stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width, ff, top, experts, glu, limit);
+        if (gated) {
+            cudaFuncSetAttribute(moe_pair_glu_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            launch_chained(moe_pair_glu_kernel<T, true>, grid, dim3(256), smem, stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width,
+                           ff, top, experts, glu, limit, in_weights);
+        } else {
+            cudaFuncSetAttribute(moe_pair_glu_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            launch_chained(moe_pair_glu_kernel<T, false>, grid, dim3(256), smem, stream, (const T*)h, ids, (const T*)w_gu, (T*)act, width,
+                           ff, top, experts, glu, limit, in_weights);
+        }
     });
     return launch_status();
 }
 
 PLLM_EXPORT int pllm_moe_pair_down(int dtype, const void* act, const void* h, const int* ids, const float* weights, const void* w_d,
                                    const void* shared, void* out, int n_tokens, int width, int ff, int top, int experts,
-                                   const float* shared_gate, cudaStream_t stream) {
+                                   const float* shared_gate, int unit_weights, cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
     if (width <= 0 || ff <= 0 || top <= 0 || experts <= 0) return PLLM_ERR_SIZE;
     if (top > MOE_MAX_TOP) return PLLM_ERR_LIMIT;
@@ -364,11 +399,11 @@ PLLM_EXPORT int pllm_moe_pair_down(int dtype, const void* act, const void* h, co
         if (n_tokens <= 4)
             launch_chained(moe_pair_down_kernel<T, 1>, dim3(n_tokens, (width + 7) / 8), dim3(256), (size_t)top * ff * sizeof(float),
                            stream, (const T*)act, (const T*)h, ids, weights, (const T*)w_d, (const T*)shared, (T*)out, width, ff, top,
-                           experts, shared_gate);
+                           experts, shared_gate, unit_weights);
         else
             launch_chained(moe_pair_down_kernel<T, 2>, dim3(n_tokens, (width + 15) / 16), dim3(256), (size_t)top * ff * sizeof(float),
                            stream, (const T*)act, (const T*)h, ids, weights, (const T*)w_d, (const T*)shared, (T*)out, width, ff, top,
-                           experts, shared_gate);
+                           experts, shared_gate, unit_weights);
     });
     return launch_status();
 }
@@ -417,7 +452,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* ids, int n_p
 
 template <typename T>
 __global__ void __launch_bounds__(256) moe_gather_kernel(const T* h, const int* slot_pair, const int* tile_expert, T* __restrict__ xs,
-                                                         int n_slots, int width, int top) {
+                                                         int n_slots, int width, int top, const float* __restrict__ in_weights) {
     pdl_launch_dependents();
     pdl_wait(KID_MOE);
     const int lane = threadIdx.x & 31, slot = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -430,6 +465,11 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const T* h, const int* 
         return;
     }
     const T* src = h + (size_t)(pair / top) * width;
+    if (in_weights) {                      // the expert reads the token times the pair's weight
+        const float w = in_weights[pair];
+        for (int c = lane; c < width; c += 32) dst[c] = from_f32<T>(to_f32(src[c]) * w);
+        return;
+    }
     if (width % N == 0) {
         for (int c = lane * N; c < width; c += 32 * N) { Vec16<T> v; v.load(src + c); v.store(dst + c); }
     } else {
@@ -440,7 +480,7 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const T* h, const int* 
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const T* y, const T* h, const int* pair_slot, const float* weights,
                                                           const T* shared, T* __restrict__ out, int width, int top,
-                                                          const float* shared_gate) {
+                                                          const float* shared_gate, int unit_weights) {
     pdl_launch_dependents();
     pdl_wait(KID_MOE);
     const int t = blockIdx.x;
@@ -450,7 +490,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* y, const T* h
         for (int k = 0; k < top; k++) {
             const int slot = pair_slot[(size_t)t * top + k];
             const float v = slot < 0 ? to_f32(h[(size_t)t * width + c]) : to_f32(y[(size_t)slot * width + c]);
-            total = fmaf(weights[(size_t)t * top + k], v, total);
+            total = fmaf((unit_weights && slot >= 0) ? 1.0f : weights[(size_t)t * top + k], v, total);
         }
         out[(size_t)t * width + c] = from_f32<T>(total);
     }
@@ -466,22 +506,22 @@ PLLM_EXPORT int pllm_moe_align(const int* ids, int n_pairs, int experts, int* sl
 }
 
 PLLM_EXPORT int pllm_moe_gather(int dtype, const void* h, const int* slot_pair, const int* tile_expert, void* xs, int n_slots,
-                                int width, int top, cudaStream_t stream) {
+                                int width, int top, const float* in_weights, cudaStream_t stream) {
     if (n_slots <= 0) return PLLM_OK;
     PLLM_DISPATCH_DTYPE(dtype, {
         launch_chained(moe_gather_kernel<T>, dim3((n_slots + 7) / 8), dim3(256), 0, stream, (const T*)h, slot_pair, tile_expert,
-                       (T*)xs, n_slots, width, top);
+                       (T*)xs, n_slots, width, top, in_weights);
     });
     return launch_status();
 }
 
 PLLM_EXPORT int pllm_moe_combine(int dtype, const void* y, const void* h, const int* pair_slot, const float* weights,
                                  const void* shared, void* out, int n_tokens, int width, int top, const float* shared_gate,
-                                 cudaStream_t stream) {
+                                 int unit_weights, cudaStream_t stream) {
     if (n_tokens <= 0) return PLLM_OK;
     PLLM_DISPATCH_DTYPE(dtype, {
         launch_chained(moe_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)y, (const T*)h, pair_slot, weights,
-                       (const T*)shared, (T*)out, width, top, shared_gate);
+                       (const T*)shared, (T*)out, width, top, shared_gate, unit_weights);
     });
     return launch_status();
 }

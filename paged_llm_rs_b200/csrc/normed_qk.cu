@@ -11,7 +11,8 @@
 //                          q to its own tensor; k | v to the token's row of the joined pool; v is the projection's v
 //                          part, or (values_are_keys) the raw key projection, neither normed nor rotated
 //                        Everything is float from the projection's values to the one rounding on the way out.
-//   gate_mul             y[t, c] *= sigmoid(g[t, c]) (kind 0) or silu(g[t, c]) (kind 1); g rows may be strided
+//   gate_mul             y[t, c] *= sigmoid(g[t, c / per]) (kind 0) or silu(g[t, c / per]) (kind 1); g rows may be strided; per 1: a
+//                        gate an entry, per = a head's size: a gate a head
 #include "common.cuh"
 
 enum : int { KID_NORMED_QK = 90 };
@@ -134,25 +135,26 @@ PLLM_EXPORT int pllm_normed_qk_kv_write(int dtype, const void* proj, int row_str
 }
 
 template <typename T>
-__global__ void gate_mul_kernel(T* y, const T* g, int g_stride, int width, long long total, int kind) {
+__global__ void gate_mul_kernel(T* y, const T* g, int g_stride, int width, long long total, int kind, int per) {
     pdl_launch_dependents();
     pdl_wait(KID_NORMED_QK);
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / width;
         const int c = (int)(i % width);
-        const float z = to_f32(g[r * g_stride + c]);
+        const float z = to_f32(g[r * g_stride + c / per]);
         const float s = nq_sigmoid(z);
         y[i] = from_f32<T>(to_f32(y[i]) * (kind == 1 ? z * s : s));
     }
 }
 
-PLLM_EXPORT int pllm_gate_mul(int dtype, void* y, const void* g, int g_stride, int n_rows, int width, int kind, cudaStream_t stream) {
+PLLM_EXPORT int pllm_gate_mul(int dtype, void* y, const void* g, int g_stride, int n_rows, int width, int kind, int per,
+                              cudaStream_t stream) {
     if (n_rows <= 0) return PLLM_OK;
-    if (width <= 0 || kind < 0 || kind > 1) return PLLM_ERR_SIZE;
+    if (width <= 0 || kind < 0 || kind > 1 || per < 1 || width % per) return PLLM_ERR_SIZE;
     PLLM_DISPATCH_DTYPE(dtype, {
         const long long total = (long long)n_rows * width;
         const int blocks = (int)min((long long)sm_count() * 8, (total + 255) / 256);
-        launch_chained(gate_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)y, (const T*)g, g_stride, width, total, kind);
+        launch_chained(gate_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)y, (const T*)g, g_stride, width, total, kind, per);
     });
     return launch_status();
 }

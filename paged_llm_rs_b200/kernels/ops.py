@@ -80,13 +80,13 @@ def lib():
         sig["pllm_latent_attention_mma_tile_tokens"] = [c_int]
         sig["pllm_latent_attention_mma_ctas_per_item"] = [c_int]
         sig["pllm_latent_attention_mma"] = [P, P, P, P, P, c_int, P, P, P] + [c_int] * 5 + [c_float, P, P]
-        sig["pllm_moe_route"] = [c_int, P, P, P, P, P] + [c_int] * 6 + [P, c_int, P, P]
+        sig["pllm_moe_route"] = [c_int, P, P, P, P, P] + [c_int] * 6 + [P, c_int, P, c_int, P]
         sig["pllm_moe_align"] = [P, c_int, c_int, P, P, P, c_int, P]
-        sig["pllm_moe_gather"] = [c_int, P, P, P, P, c_int, c_int, c_int, P]
-        sig["pllm_moe_combine"] = [c_int, P, P, P, P, P, P, c_int, c_int, c_int, P, P]
+        sig["pllm_moe_gather"] = [c_int, P, P, P, P, c_int, c_int, c_int, P, P]
+        sig["pllm_moe_combine"] = [c_int, P, P, P, P, P, P, c_int, c_int, c_int, P, c_int, P]
         sig["pllm_gemm_tcgen05_grouped"] = [P, P, P, c_int, c_int, c_int, c_int, c_float, P, c_int, P, P]
-        sig["pllm_moe_pair_glu"] = [c_int, P, P, P, P] + [c_int] * 6 + [c_float, P]
-        sig["pllm_moe_pair_down"] = [c_int, P, P, P, P, P, P, P] + [c_int] * 5 + [P, P]
+        sig["pllm_moe_pair_glu"] = [c_int, P, P, P, P] + [c_int] * 6 + [c_float, c_int, P, P]
+        sig["pllm_moe_pair_down"] = [c_int, P, P, P, P, P, P, P] + [c_int] * 5 + [P, c_int, P]
         sig["pllm_embed_norm32"] = [c_int, P, P, P, P, c_int, c_int, c_int, c_float, P, P]
         sig["pllm_add_scaled_norm32"] = [c_int, P, P, c_float, P, P, P, c_int, c_int, c_float, P]
         sig["pllm_add_scaled32"] = [c_int, P, P, c_float, c_ll, P]
@@ -103,7 +103,11 @@ def lib():
         sig["pllm_scaled_sum2"] = [c_int, P, P, c_float, c_float, P, c_ll, P]
         sig["pllm_swiglu_bias"] = [c_int, P, P, P, c_int, c_int, c_int, c_float, P]
         sig["pllm_normed_qk_kv_write"] = [c_int, P, c_int, c_int, c_int, P, P, P, c_int, c_float, c_float, c_int, P, c_int, P, P, P] + [c_int] * 7 + [c_ll, P, P]
-        sig["pllm_gate_mul"] = [c_int, P, P, c_int, c_int, c_int, c_int, P]
+        sig["pllm_gate_mul"] = [c_int, P, P, c_int, c_int, c_int, c_int, c_int, P]
+        sig["pllm_unary_act"] = [c_int, P, c_ll, c_int, P]
+        sig["pllm_conv_rope_kv_write"] = [c_int, P, c_int, P, P, c_int, P, c_int, c_int, P, c_ll, P, c_int, P, P, P, P] + [c_int] * 6 + [c_ll, P, P]
+        sig["pllm_diff_combine"] = [c_int, P, P, c_int, P] + [c_int] * 4 + [c_float] * 3 + [P]
+        sig["pllm_latent_rope_write"] = [c_int, P, c_int, P, c_float, P, c_int, P, P, P, P, P, P, P] + [c_int] * 6 + [c_ll, P, P]
         sig["pllm_mlstm_mix"] = [c_int, P, c_int, P, P, P, c_float, P, P, c_int, c_int, P, c_ll, P, P, P, P] + [c_int] * 4 + [c_float, P]
         sig["pllm_delta_mix"] = [c_int, P, c_int, P, P, P, P, P, P, c_int, c_int, P, c_ll, P, P, P] + [c_int] * 6 + [c_float, P]
         wide = {"pllm_mlstm_state_floats": [c_int] * 3, "pllm_delta_state_floats": [c_int] * 5}
@@ -804,11 +808,26 @@ def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_tables: torch.Te
 
 # ---- mixture of experts (csrc/moe.cu) -----------------------------------------------------------------------
 
+ROUTER_SCORINGS = {"softmax": 0, "sigmoid": 1}
+UNARY_KINDS = {"none": 0, "squared_relu": 1}      # one-argument activations of feed-forwards without a gate (common.cuh)
+
+
+def _expert_act(act: str, gated: bool) -> int:
+    if gated:
+        return _glu(act)
+    if act not in UNARY_KINDS:
+        raise KernelError(f"activation {act!r} of experts without a gate is not known; known: {sorted(UNARY_KINDS)}")
+    return UNARY_KINDS[act]
+
+
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
-              bias: Optional[torch.Tensor] = None, extra: int = 0):
+              bias: Optional[torch.Tensor] = None, extra: int = 0, scoring: str = "softmax", renormalize: bool = True):
     """The router: (ids int32 [T, top], weights float32 [T, top]).  w_router float32 [outputs + extra, width].
     ``bias`` (float32 [outputs]) is added to the logits.  With ``extra`` the matrix carries that many further rows
-    behind the router's, and their products with h come back as a third value, float32 [T, extra]."""
+    behind the router's, and their products with h come back as a third value, float32 [T, extra].  ``scoring``: "softmax"
+    over all logits, or "sigmoid" of each; ``renormalize`` False: a chosen output's weight is its score itself."""
+    if scoring not in ROUTER_SCORINGS:
+        raise KernelError(f"moe_route: scoring {scoring!r} is not known; known: {sorted(ROUTER_SCORINGS)}")
     _dev(h, w_router, correction, bias)
     _f32(w_router, "w_router"); _f32(correction, "correction"); _f32(bias, "bias")
     T, W = h.shape
@@ -819,34 +838,37 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
     weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
     more = torch.empty((T, extra), dtype=torch.float32, device=h.device) if extra else None
     _check(lib().pllm_moe_route(_code(h), _ptr(h), _ptr(w_router), _ptr(correction), _ptr(ids), _ptr(weights), T, W, E,
-                                int(top), int(groups), int(keep), _ptr(bias), int(extra), _ptr(more), _stream()), "moe_route")
+                                int(top), int(groups), int(keep), _ptr(bias), int(extra), _ptr(more),
+                                ROUTER_SCORINGS[scoring] | (0 if renormalize else 2), _stream()), "moe_route")
     return (ids, weights, more) if extra else (ids, weights)
 
 
 def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
                     shared: Optional[torch.Tensor], act: str = "silu", limit: float = 0.0,
-                    shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    shared_gate: Optional[torch.Tensor] = None, gated: bool = True, weight_input: bool = False) -> torch.Tensor:
     """sum_k weights[t, k] * expert_{ids[t, k]}(h[t]) (+ shared[t]); an id at or above the experts with tensors is the
     identity.  w_gu [experts, 2 ff, width] (gate rows, then up rows), w_d [experts, width, ff].  The weight-streaming form.
-    ``act``, ``limit``: the experts' gated activation.  ``shared_gate`` (float32 [T]): shared[t] is multiplied by its sigmoid."""
+    ``act``, ``limit``: the experts' gated activation.  ``shared_gate`` (float32 [T]): shared[t] is multiplied by its sigmoid.
+    ``gated`` False: experts down(act(up h)) with w_gu [experts, ff, width] and a one-argument ``act``.  ``weight_input``: the
+    sum is over expert(weights[t, k] * h[t]) instead."""
     _dev(h, ids, weights, w_gu, w_d, shared, shared_gate)
     _i32(ids, "ids"); _f32(weights, "weights"); _f32(shared_gate, "shared_gate")
     if shared_gate is not None and shared_gate.numel() != h.shape[0]:
         raise KernelError("moe_experts_few: the shared expert's gate must hold one number a token")
     T, W = h.shape
     E, two_ff, _ = w_gu.shape
-    ff, top = two_ff // 2, ids.shape[1]
-    if w_gu.shape != (E, 2 * ff, W) or w_d.shape != (E, W, ff) or w_gu.dtype != h.dtype or w_d.dtype != h.dtype:
+    ff, top = (two_ff // 2 if gated else two_ff), ids.shape[1]
+    if w_gu.shape != (E, (2 if gated else 1) * ff, W) or w_d.shape != (E, W, ff) or w_gu.dtype != h.dtype or w_d.dtype != h.dtype:
         raise KernelError("moe_experts_few: expert weights do not fit")
     if shared is not None and (shared.shape != h.shape or shared.dtype != h.dtype):
         raise KernelError("moe_experts_few: the shared expert's output must have h's shape and dtype")
     acts = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
     out = torch.empty_like(h)
     L = lib()
-    _check(L.pllm_moe_pair_glu(_code(h), _ptr(h), _ptr(ids), _ptr(w_gu), _ptr(acts), T, W, ff, top, E, _glu(act), float(limit),
-                               _stream()), "moe_pair_glu")
+    _check(L.pllm_moe_pair_glu(_code(h), _ptr(h), _ptr(ids), _ptr(w_gu), _ptr(acts), T, W, ff, top, E, _expert_act(act, gated),
+                               float(limit), 1 if gated else 0, _ptr(weights) if weight_input else None, _stream()), "moe_pair_glu")
     _check(L.pllm_moe_pair_down(_code(h), _ptr(acts), _ptr(h), _ptr(ids), _ptr(weights), _ptr(w_d), _ptr(shared), _ptr(out),
-                                T, W, ff, top, E, _ptr(shared_gate), _stream()), "moe_pair_down")
+                                T, W, ff, top, E, _ptr(shared_gate), 1 if weight_input else 0, _stream()), "moe_pair_down")
     return out
 
 
@@ -856,25 +878,28 @@ def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
 MOE_GROUPED_MIN_TOKENS = int(os.environ.get("PAGED_LLM_MOE_GROUPED_MIN", "48"))
 
 
-def moe_grouped_takes(h: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor) -> bool:
+def moe_grouped_takes(h: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor, gated: bool = True) -> bool:
     if h.dtype != torch.bfloat16 or h.shape[0] < MOE_GROUPED_MIN_TOKENS or TCGEN05_GEMM < 1:
         return False
     E, two_ff, W = w_gu.shape
+    ff = two_ff // 2 if gated else two_ff
     L = lib()
-    return bool(L.pllm_gemm_tcgen05_supports(128, two_ff // 2, W, 1)) and bool(L.pllm_gemm_tcgen05_supports(128, W, two_ff // 2, 0))
+    return bool(L.pllm_gemm_tcgen05_supports(128, ff, W, 1 if gated else 0)) and bool(L.pllm_gemm_tcgen05_supports(128, W, ff, 0))
 
 
 def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
                         shared: Optional[torch.Tensor], status: Optional[torch.Tensor] = None, act: str = "silu",
-                        limit: float = 0.0, shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        limit: float = 0.0, shared_gate: Optional[torch.Tensor] = None, gated: bool = True,
+                        weight_input: bool = False) -> torch.Tensor:
     """The same sum as ``moe_experts_few`` by sorting the (token, expert) pairs by expert, two grouped tensor-core
-    products (the first with the gated activation in its epilogue) and a weighted combine."""
+    products (the first with the activation in its epilogue) and a weighted combine; with ``weight_input`` the gathered
+    rows are multiplied by their weights instead."""
     _dev(h, ids, weights, w_gu, w_d, shared, shared_gate)
     _i32(ids, "ids"); _f32(weights, "weights"); _f32(shared_gate, "shared_gate")
     T, W = h.shape
     E, two_ff, _ = w_gu.shape
-    ff, top = two_ff // 2, ids.shape[1]
-    if not moe_grouped_takes(h, w_gu, w_d) or w_gu.shape != (E, 2 * ff, W) or w_d.shape != (E, W, ff):
+    ff, top = (two_ff // 2 if gated else two_ff), ids.shape[1]
+    if not moe_grouped_takes(h, w_gu, w_d, gated) or w_gu.shape != (E, (2 if gated else 1) * ff, W) or w_d.shape != (E, W, ff):
         raise KernelError("moe_experts_grouped: shapes or dtypes the grouped product does not take")
     n_pairs = T * top
     max_tiles = -(-n_pairs // 128) + E
@@ -891,23 +916,25 @@ def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tenso
     L = lib()
     _check(L.pllm_moe_align(_ptr(ids), n_pairs, E, _ptr(slot_pair), _ptr(pair_slot), _ptr(tile_expert), max_tiles, _stream()),
            "moe_align")
-    _check(L.pllm_moe_gather(_code(h), _ptr(h), _ptr(slot_pair), _ptr(tile_expert), _ptr(xs), slots, W, top, _stream()), "moe_gather")
-    _check(L.pllm_gemm_tcgen05_grouped(_ptr(xs), _ptr(w_gu), _ptr(acts), slots, ff, W, 1 + _glu(act), float(limit), _ptr(tile_expert),
+    _check(L.pllm_moe_gather(_code(h), _ptr(h), _ptr(slot_pair), _ptr(tile_expert), _ptr(xs), slots, W, top,
+                             _ptr(weights) if weight_input else None, _stream()), "moe_gather")
+    _check(L.pllm_gemm_tcgen05_grouped(_ptr(xs), _ptr(w_gu), _ptr(acts), slots, ff, W,
+                                       1 + _glu(act) if gated else -_expert_act(act, False), float(limit), _ptr(tile_expert),
                                        E, _ptr(st), _stream()), "gemm_tcgen05_grouped (gate/up)")
     _check(L.pllm_gemm_tcgen05_grouped(_ptr(acts), _ptr(w_d), _ptr(y), slots, W, ff, 0, 0.0, _ptr(tile_expert), E, _ptr(st), _stream()),
            "gemm_tcgen05_grouped (down)")
     _check(L.pllm_moe_combine(_code(h), _ptr(y), _ptr(h), _ptr(pair_slot), _ptr(weights), _ptr(shared), _ptr(out), T, W, top,
-                              _ptr(shared_gate), _stream()), "moe_combine")
+                              _ptr(shared_gate), 1 if weight_input else 0, _stream()), "moe_combine")
     return out
 
 
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor,
                 shared: Optional[torch.Tensor], status: Optional[torch.Tensor] = None, act: str = "silu", limit: float = 0.0,
-                shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                shared_gate: Optional[torch.Tensor] = None, gated: bool = True, weight_input: bool = False) -> torch.Tensor:
     """The routed experts' weighted sum (+ the shared expert's output), by the form that fits the step."""
-    if moe_grouped_takes(h, w_gu, w_d):
-        return moe_experts_grouped(h, ids, weights, w_gu, w_d, shared, status, act, limit, shared_gate)
-    return moe_experts_few(h, ids, weights, w_gu, w_d, shared, act, limit, shared_gate)
+    if moe_grouped_takes(h, w_gu, w_d, gated):
+        return moe_experts_grouped(h, ids, weights, w_gu, w_d, shared, status, act, limit, shared_gate, gated, weight_input)
+    return moe_experts_few(h, ids, weights, w_gu, w_d, shared, act, limit, shared_gate, gated, weight_input)
 
 
 # ---- a float32 stream with pre-norm blocks (csrc/stream32.cu) ----------------------------------------------------
@@ -1191,15 +1218,17 @@ def normed_qk_kv_write(proj: torch.Tensor, k_off: int, v_off: int, q_out: torch.
 GATE_KINDS = {"sigmoid": 0, "silu": 1}
 
 
-def gate_mul(y: torch.Tensor, gate: torch.Tensor, kind: str = "sigmoid") -> torch.Tensor:
-    """y[t, c] *= sigmoid(gate[t, c]) (or silu), in place; ``gate`` may be a column range of a wider tensor."""
+def gate_mul(y: torch.Tensor, gate: torch.Tensor, kind: str = "sigmoid", per: int = 1) -> torch.Tensor:
+    """y[t, c] *= sigmoid(gate[t, c // per]) (or silu), in place; ``gate`` may be a column range of a wider tensor.
+    ``per`` 1: a gate an entry; a head's size: a gate a head."""
     _dev(y)
     if kind not in GATE_KINDS:
         raise KernelError(f"gate_mul: kind {kind!r} is not known; known: {sorted(GATE_KINDS)}")
-    if not gate.is_cuda or gate.shape != y.shape or gate.dtype != y.dtype or gate.stride(1) != 1 or y.dim() != 2:
-        raise KernelError("gate_mul: the gate must have y's shape and dtype, with unit inner stride")
-    _check(lib().pllm_gate_mul(_code(y), _ptr(y), _ptr(gate), gate.stride(0), y.shape[0], y.shape[1], GATE_KINDS[kind], _stream()),
-           "gate_mul")
+    if y.dim() != 2 or per < 1 or y.shape[1] % per or not gate.is_cuda or gate.shape != (y.shape[0], y.shape[1] // per) \
+            or gate.dtype != y.dtype or gate.stride(1) != 1:
+        raise KernelError("gate_mul: the gate must have y's rows and dtype, one entry for every ``per`` of y's, with unit inner stride")
+    _check(lib().pllm_gate_mul(_code(y), _ptr(y), _ptr(gate), gate.stride(0), y.shape[0], y.shape[1], GATE_KINDS[kind], int(per),
+                               _stream()), "gate_mul")
     return y
 
 
@@ -1277,3 +1306,139 @@ def delta_mix(u: torch.Tensor, conv_w: torch.Tensor, ba: torch.Tensor, a_log: to
                                 _ptr(y_buf), _ptr(out), T, heads, kv_heads, dim, vdim, taps, float(eps), _stream()),
            "delta_mix", launches=3)
     return out
+
+
+# ---- feed-forwards without a gate (csrc/elementwise.cu, csrc/gemm_tcgen05.cu) ---------------------------------------------
+
+def unary_act(x: torch.Tensor, act: str) -> torch.Tensor:
+    """x = act(x) in place, for a one-argument activation of ``UNARY_KINDS``."""
+    _dev(x)
+    if act not in UNARY_KINDS:
+        raise KernelError(f"unary_act: activation {act!r} is not known; known: {sorted(UNARY_KINDS)}")
+    if not x.is_contiguous():
+        raise KernelError("unary_act: x must be contiguous")
+    _check(lib().pllm_unary_act(_code(x), _ptr(x), x.numel(), UNARY_KINDS[act], _stream()), "unary_act")
+    return x
+
+
+def linear_act(x: torch.Tensor, weight: torch.Tensor, act: str, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(x W^T) for a one-argument activation: the first half of a feed-forward without a gate.  Many rows in bfloat16:
+    the tcgen05 product with the activation in its epilogue; otherwise the product, then the activation in place."""
+    if act not in UNARY_KINDS:
+        raise KernelError(f"linear_act: activation {act!r} is not known; known: {sorted(UNARY_KINDS)}")
+    N, K = weight.shape
+    if x.shape[-1] != K:
+        raise KernelError(f"linear_act: input width {x.shape[-1]} does not fit a weight of {tuple(weight.shape)}")
+    if TCGEN05_GEMM >= 1 and x.shape[0] >= TCGEN05_MIN_M and gemm_tcgen05_takes(x, weight, N, False):
+        _dev(x, weight)
+        out = torch.empty((x.shape[0], N), dtype=torch.bfloat16, device=x.device)
+        st = status if status is not None else gemm_status(x.device)
+        _check(lib().pllm_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), x.shape[0], N, K, -UNARY_KINDS[act], 0.0, _ptr(st),
+                                       _stream()), "gemm_tcgen05 (activation)")
+        return out
+    return unary_act(linear(x, weight, status=status), act)
+
+
+# ---- differential attention and latent attention with a rotated key part (csrc/diff_attention.cu) -------------------------
+
+def conv_state_floats(channels: int, taps: int) -> int:
+    """Floats of a request's state slot for a short convolution: each channel's last taps - 1 inputs (at least one float)."""
+    return max(1, (taps - 1) * channels)
+
+
+def conv_rope_kv_write(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_w: torch.Tensor, segments: torch.Tensor,
+                       max_segment_tokens: int, state: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int,
+                       positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor, kv_pool: Optional[torch.Tensor],
+                       q_heads: int, k_heads: int, maps: int, dk: int, dv: int, status: torch.Tensor) -> torch.Tensor:
+    """From a projection's [q | k | v] channels (the first columns of ``proj``) to the attention's inputs: + bias, a causal
+    convolution of conv_w.shape[1] taps a channel over each segment's tokens (earlier inputs from the segment's state slot,
+    which then takes this step's last ones), the first ``rot`` entries of each q and k head turned (entry i with i + rot / 2),
+    q to ``q_out`` [T, q_heads dk], k | v to the token's rows of the joined pool [pages, k_heads, page_size, dk + dv].  With
+    ``maps`` > 1 a kv head has that many keys a token, each a pool row of its own followed by the kv head's one value."""
+    _dev(bias, conv_w, segments, state, inv_freq, positions, slots, q_out, kv_pool, status)
+    if not proj.is_cuda:
+        raise KernelError("conv_rope_kv_write: proj is not on a CUDA device")
+    _segments_ok(segments, "conv_rope_kv_write")
+    for t, n in ((bias, "bias"), (conv_w, "conv_w"), (state, "state"), (inv_freq, "inv_freq")):
+        _f32(t, n)
+    _i32(positions, "positions"); _i32(slots, "slots")
+    T = proj.shape[0]
+    channels = (q_heads + k_heads) * dk + (k_heads // maps) * dv
+    taps = conv_w.shape[1]
+    if proj.dim() != 2 or proj.shape[1] < channels or proj.stride(1) != 1 or conv_w.shape != (channels, taps) or not conv_w.is_contiguous():
+        raise KernelError("conv_rope_kv_write: proj must hold the channels in its first columns, conv_w be [channels, taps]")
+    if bias is not None and bias.numel() != channels:
+        raise KernelError("conv_rope_kv_write: one bias a channel")
+    if q_out.shape != (T, q_heads * dk) or q_out.dtype != proj.dtype or not q_out.is_contiguous():
+        raise KernelError("conv_rope_kv_write: q_out must be [T, q_heads dk] of proj's dtype")
+    if state.dim() != 2 or state.shape[1] < conv_state_floats(channels, taps):
+        raise KernelError("conv_rope_kv_write: the state slots are too small")
+    if rot and (inv_freq is None or inv_freq.numel() != rot // 2):
+        raise KernelError("conv_rope_kv_write: one frequency for every rotated pair")
+    pool_rows, page_size = 0, 1
+    if kv_pool is not None:
+        if kv_pool.dim() != 4 or kv_pool.shape[1] != k_heads or kv_pool.shape[3] != dk + dv or kv_pool.dtype != proj.dtype \
+                or not kv_pool.is_contiguous():
+            raise KernelError(f"conv_rope_kv_write: the pool must be [pages, {k_heads}, page_size, {dk + dv}] of proj's dtype")
+        page_size, pool_rows = kv_pool.shape[2], kv_pool.shape[0] * kv_pool.shape[2]
+    _check(lib().pllm_conv_rope_kv_write(_code(proj), _ptr(proj), proj.stride(0), _ptr(bias), _ptr(conv_w), taps, _ptr(segments),
+                                         segments.shape[0], int(max_segment_tokens), _ptr(state), state.stride(0), _ptr(inv_freq),
+                                         int(rot), _ptr(positions), _ptr(slots), _ptr(q_out), _ptr(kv_pool), q_heads, k_heads, maps,
+                                         dk, dv, page_size, pool_rows, _ptr(status), _stream()),
+           "conv_rope_kv_write", launches=2 if taps > 1 else 1)
+    return q_out
+
+
+def diff_combine(a: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, heads: int, group: int, dv: int, lam: float, post: float,
+                 eps: float) -> torch.Tensor:
+    """out[t, h] = post * sigmoid(gate[t, h]) * (a1 - lam a2) over its root mean square, for a [T, 2 heads, dv] whose heads are
+    ordered [kv head][map][head of the group] (``group`` heads a kv head); ``gate`` [T, heads] may be a column range."""
+    _dev(a, out)
+    if not gate.is_cuda:
+        raise KernelError("diff_combine: the gate is not on a CUDA device")
+    T = a.shape[0]
+    if a.numel() != T * 2 * heads * dv or out.shape != (T, heads * dv) or out.dtype != a.dtype or not a.is_contiguous():
+        raise KernelError("diff_combine: a must be [T, 2 heads, dv] and out [T, heads dv] of one dtype")
+    if gate.shape != (T, heads) or gate.dtype != a.dtype or gate.stride(1) != 1:
+        raise KernelError("diff_combine: the gate must be [T, heads] of a's dtype with unit inner stride")
+    _check(lib().pllm_diff_combine(_code(a), _ptr(a), _ptr(gate), gate.stride(0), _ptr(out), T, heads, group, dv, float(lam),
+                                   float(post), float(eps), _stream()), "diff_combine")
+    return out
+
+
+def latent_rope_write(down: Optional[torch.Tensor], gain: Optional[torch.Tensor], eps: float, q: torch.Tensor, q_rows: torch.Tensor,
+                      pool: Optional[torch.Tensor], slots: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                      heads: int, dim: int, rot_dim: int, rot: int, kv_rank: int, status: torch.Tensor,
+                      row_out: Optional[torch.Tensor] = None, carried: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``down`` [T, kv_rank + rot_dim] (or None: no rows are made): the latent over its root mean square times ``gain`` and the
+    key part with its first ``rot`` entries turned pairwise go side by side into the token's row of ``pool``
+    [pages, page_size, kv_rank + rot_dim], and to ``row_out`` [T, kv_rank + rot_dim] if given.  Without ``down``, rows made
+    that way earlier in the step (``carried``) are stored as they are.  ``q`` [T, heads (dim + rot_dim)] (may be a column range): each head's last
+    rot_dim entries, turned likewise, go to the last rot_dim entries of ``q_rows`` [T, heads, kv_rank + rot_dim]."""
+    _dev(gain, q_rows, pool, slots, positions, inv_freq, status, row_out, carried)
+    if not q.is_cuda or (down is not None and not down.is_cuda):
+        raise KernelError("latent_rope_write: q or down is not on a CUDA device")
+    _f32(gain, "gain"); _f32(inv_freq, "inv_freq"); _i32(slots, "slots"); _i32(positions, "positions")
+    T, width = q.shape[0], kv_rank + rot_dim
+    for t, n in ((row_out, "row_out"), (carried, "carried")):
+        if t is not None and (t.shape != (T, width) or t.dtype != q.dtype or not t.is_contiguous()):
+            raise KernelError(f"latent_rope_write: {n} must be [T, kv_rank + rot_dim] of q's dtype")
+    if down is not None and carried is not None:
+        raise KernelError("latent_rope_write: rows are made from down or carried from an earlier layer, not both")
+    if q.shape[1] != heads * (dim + rot_dim) or q.stride(1) != 1 or q_rows.shape != (T, heads, width) or not q_rows.is_contiguous() \
+            or q_rows.dtype != q.dtype:
+        raise KernelError("latent_rope_write: q must be [T, heads (dim + rot_dim)] and q_rows [T, heads, kv_rank + rot_dim]")
+    if down is not None and (down.shape != (T, width) or down.stride(1) != 1 or down.dtype != q.dtype or gain is None or gain.numel() != kv_rank):
+        raise KernelError("latent_rope_write: down must be [T, kv_rank + rot_dim] of q's dtype, with a gain of kv_rank entries")
+    if rot and (inv_freq is None or inv_freq.numel() != rot // 2):
+        raise KernelError("latent_rope_write: one frequency for every rotated pair")
+    pool_rows = 0
+    if pool is not None and (down is not None or carried is not None):
+        if pool.dim() != 3 or pool.shape[2] != width or pool.dtype != q.dtype or not pool.is_contiguous():
+            raise KernelError("latent_rope_write: the pool must be [pages, page_size, kv_rank + rot_dim] of q's dtype")
+        pool_rows = pool.shape[0] * pool.shape[1]
+    _check(lib().pllm_latent_rope_write(_code(q), _ptr(down), down.stride(0) if down is not None else 0, _ptr(gain), float(eps), _ptr(q),
+                                        q.stride(0), _ptr(q_rows), _ptr(pool) if pool_rows else None, _ptr(row_out), _ptr(carried), _ptr(slots),
+                                        _ptr(positions), _ptr(inv_freq), T, heads, dim, rot_dim, int(rot), kv_rank, pool_rows,
+                                        _ptr(status), _stream()), "latent_rope_write")
+    return q_rows

@@ -12,7 +12,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from . import (attention, block, embedding, feed_forward, latent_attention, mamba2, matrix_memory, norm,  # noqa: F401  (register the parts)
+from . import (attention, block, diff_attention, embedding, feed_forward, latent_attention, mamba2, matrix_memory, norm,  # noqa: F401  (register the parts)
                normed_attention, parallel, position, routed_feed_forward, sink_attention)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Runtime, StepState,
                    make)

@@ -76,11 +76,16 @@ class StreamRMSNorm(RMSNorm):
 class ScaledStreamRMSNorm(RMSNorm):
     """RMSNorm in a pre-norm decoder whose residual stream stays float32 and whose sublayer outputs are multiplied by
     one constant ``mult`` as they are added: ``add_norm`` does stream += mult * delta (in place) and norms the sum into
-    the compute dtype, in one kernel."""
+    the compute dtype, in one kernel.  ``one_plus``: the file holds the gain's distance from one."""
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.mult = float(spec.params.get("mult", 1.0))
+        self.one_plus = bool(spec.params.get("one_plus", False))     # the file holds gain - 1
+
+    def bind(self, tensors):
+        w = tensors[self._gain_name()]
+        self.gain = (w + 1.0) if self.one_plus else w
 
     def forward(self, x, rows=None):
         return self.add_norm(x, None, rows)
