@@ -113,7 +113,8 @@ def latent_rows(h, w, p, m, eps):
     r, dr = m["kv_rank"], m["rot_dim"]
     down = h @ w[p + ".dkv"].T
     c = rms_unit(down[:, :r], eps) * w[p + ".dkv.norm"]
-    kr = rotate_pairs(down[:, r:].view(T, 1, dr), m["rot"]["dims"], m["rot"]["base"]).view(T, dr)
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    kr = rotate_pairs(down[:, r:].view(T, 1, dr), rot["dims"], rot["base"]).view(T, dr)
     return c, kr
 
 
@@ -124,7 +125,8 @@ def latent_attention(h, w, p, m, eps, kept=None):
     H, d, dr, dv = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
     c, kr = kept if kept is not None else latent_rows(h, w, p, m, eps)
     q = (h @ w[p + ".q"].T).view(T, H, d + dr)
-    qn, qr = q[..., :d], rotate_pairs(q[..., d:], m["rot"]["dims"], m["rot"]["base"])
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    qn, qr = q[..., :d], rotate_pairs(q[..., d:], rot["dims"], rot["base"])
     kn = (c @ w[p + ".uk"].T).view(T, H, d)
     v = (c @ w[p + ".uv"].T).view(T, H, dv)
     gate = torch.sigmoid(h @ w[p + ".g"].T)
