@@ -959,6 +959,228 @@ def matrix_kernels(z, pk):
     return out
 
 
+# ---- the differential-attention / matrix-LSTM / latent-attention decoder with squared-relu experts (Tebozen) ------------
+# Sizes that resemble real layers, at the widths of the 0.6B and of a 2B-class shape: differential attention of eight or
+# sixteen heads over half as many kv heads, two maps of 64 key entries a head over values of 128, behind convolutions of
+# four taps, in a window of 1024 tokens, every map wholly rotated; a matrix LSTM of width / 256 heads with keys of 128 and
+# values of 256 entries; latent attention of sixteen heads with 64 unrotated and 64 rotated key entries over a cached row of
+# 192 + 64 values; every layer has sixteen or thirty-two experts without gates, four a token, and a shared expert.  Layers
+# go attention, matrix LSTM, latent attention, matrix LSTM; the second latent layer attends over the first one's cache.
+# The other model is the Bumisun shape of the same width, layers, experts and vocabulary.
+TEBOZEN_SIZES = {
+    "1024": dict(width=1024, heads=8, kv_heads=4, dim=64, vdim=128, conv=4, window=1024, rot=64, m_heads=4, m_dim=128, m_vdim=256,
+                 l_heads=16, l_dim=64, l_rot=64, l_vdim=64, kv_rank=192, experts=16, top=4, expert_ff=768, shared_ff=768),
+    "2048": dict(width=2048, heads=16, kv_heads=8, dim=64, vdim=128, conv=4, window=1024, rot=64, m_heads=8, m_dim=128, m_vdim=256,
+                 l_heads=16, l_dim=64, l_rot=64, l_vdim=64, kv_rank=192, experts=32, top=4, expert_ff=1536, shared_ff=1536),
+}
+
+
+def tebozen_config(z, layers):
+    att = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], conv=z["conv"], diff=0.3, scale=z["dim"] ** -0.5,
+               mask=dict(size=z["window"]), rot=dict(dims=z["rot"], base=10000.0))
+    lstm = dict(heads=z["m_heads"], dim=z["m_dim"], vdim=z["m_vdim"], gate_cap=15.0)
+    lat = dict(heads=z["l_heads"], dim=z["l_dim"], rot_dim=z["l_rot"], vdim=z["l_vdim"], kv_rank=z["kv_rank"],
+               scale=(z["l_dim"] + z["l_rot"]) ** -0.5, rot=dict(dims=z["l_rot"], base=10000.0))
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), shared=dict(ff=z["shared_ff"]), router=dict(experts=z["experts"], top=z["top"]))
+    out, first_latent = [], None
+    for i in range(layers):
+        kind = ("attention", "mlstm", "latent_attention", "mlstm")[i % 4]
+        mixer = dict(att if kind == "attention" else lstm if kind == "mlstm" else lat)
+        if kind == "latent_attention":
+            if first_latent is None:
+                first_latent = i
+            else:
+                mixer["kv_from"] = first_latent
+        out.append(dict(type=kind, mixer=mixer, mlp=moe))
+    return dict(architecture="Tebozen", vocab=LATENT_VOCAB, width=z["width"], norm=dict(eps=1e-6), embedding=dict(scale=1.0), layers=out)
+
+
+def tebozen_beside_hybrid(size, layers, pk, clocks, steps, warmup, which="both"):
+    """Decode (batch 1, 8, 64 at context 4096) and the 2048-token prefill of the Tebozen shape ``size`` and of the Bumisun
+    shape of the same width, layers, experts and vocabulary (a routed feed-forward in every layer): tokens a second, side by
+    side; then Tebozen's own kernels alone beside their like kernels."""
+    import gc
+    import torch
+    from paged_llm_rs_b200 import Engine, write_random_model
+
+    z = TEBOZEN_SIZES[size]
+    hz = dict(HYBRID_SIZES[size], experts=z["experts"], top=z["top"], expert_ff=z["expert_ff"], shared_ff=z["shared_ff"])
+    hybrid = hybrid_config(hz, layers)
+    routed = next(L["mlp"] for L in hybrid["layers"] if L["mlp"]["kind"] == "moe")
+    for L in hybrid["layers"]:
+        L["mlp"] = routed
+    out = dict(size=size, layers=layers, vocab=LATENT_VOCAB, tebozen=dict(z))
+    for name, cfg in (("tebozen", tebozen_config(z, layers)), ("bumisun", hybrid)):
+        if which not in ("both", name):
+            continue
+        tmp = tempfile.mkdtemp(prefix="pllm_bench_", dir=scratch_dir())
+        try:
+            model_dir = write_random_model(os.path.join(tmp, "model"), cfg, 0, device="cuda")
+            ctx = 4096
+            pages = 64 * (ctx // PAGE + 4) + (PREFILL_TOKENS + 1024) // PAGE + 64
+            eng = Engine(model_dir, dtype="bfloat16", block_size=PAGE, blocks=pages, max_batch=64, chunk=PREFILL_TOKENS,
+                         prefix_cache=False)
+            shutil.rmtree(tmp, ignore_errors=True)
+            runner = eng.runner
+            for g in runner.cache.groups:
+                if g.pool is not None:
+                    g.pool.normal_(0.0, 1.0)
+            res = dict(weight_bytes=runner.weight_bytes(), cache_bytes_a_token=runner.cache.bytes_per_token())
+            for b in (1, 8, 64):
+                ms, launches, spread = decode_point(runner, b, ctx, max(5, steps // 2), warmup, clocks, repeats=4)
+                res[f"decode_b{b}_tok_s"] = round(b / (spread["median_ms"] / 1e3), 1)
+                res[f"decode_b{b}_ms"] = spread["median_ms"]
+                res[f"decode_b{b}_launches"] = launches
+            pms, _ = prefill_point(runner, LATENT_VOCAB, clocks, repeats=4)
+            res["prefill_ms"] = round(pms, 3)
+            res["prefill_tok_s"] = round(PREFILL_TOKENS / (pms / 1e3), 1)
+            out[name] = res
+            del eng, runner
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+            gc.collect()
+            torch.cuda.empty_cache()
+    out["kernels"] = tebozen_kernels(z, pk)
+    like = hybrid_kernels(HYBRID_SIZES[size], pk)
+    out["kernels"].update({f"bumisun_{k}": v for k, v in like.items() if not k.startswith("qwen3_")})
+    return out
+
+
+def tebozen_kernels(z, pk):
+    """Tebozen's own kernels alone, at the sizes of ``z``, each beside its like kernel of another design where that is not
+    among Bumisun's: device time (CUDA events, the median of nine after three warm-ups, an L2 flush before each, the cache
+    pools larger than L2 where a model's would be), the algorithmic bytes and FLOPs, and the fraction of the measured copy
+    bandwidth or bfloat16 product rate they come to."""
+    import numpy as np
+    import torch
+    from paged_llm_rs_b200.kernels import attention_plan, ops
+    from paged_llm_rs_b200.parts.base import AttentionWork
+
+    dev, bf = "cuda", torch.bfloat16
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    target = 2 * ops.sm_count()
+    out = {}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(9):
+            flush_l2()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    def note(name, ms, nbytes, flops):
+        r = dict(us=round(ms * 1e3, 2), mbytes=round(nbytes / 1e6, 2), gflop=round(flops / 1e9, 3),
+                 hbm_frac=round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                 bf16_frac=round(flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4))
+        r["frac_of_slower_bound"] = round(max(r["hbm_frac"], r["bf16_frac"]), 4)
+        out[name] = r
+
+    def plan(segs, tile, ctas, window):
+        work, red, parts = attention_plan.plan_attention(segs, tile, window, ctas, target)
+        wd = torch.from_numpy(np.ascontiguousarray(work)).reshape(-1, 8).to(dev) if len(work) else torch.zeros(1, 8, dtype=torch.int32, device=dev)
+        rd = torch.from_numpy(np.ascontiguousarray(red)).reshape(-1, 4).to(dev) if len(red) else torch.zeros(1, 4, dtype=torch.int32, device=dev)
+        singles = all(n == 1 for _, n, _ in segs)
+        return lambda heads, hd: AttentionWork(wd, torch.tensor([len(work)], dtype=torch.int32, device=dev), max(len(work), 1), rd,
+                                                torch.tensor([len(red)], dtype=torch.int32, device=dev), len(red),
+                                                torch.zeros(max(parts, 1), heads, hd, device=dev), torch.zeros(max(parts, 1), heads, 2, device=dev),
+                                                kinds=1 if singles else 2, many_splits=attention_plan.many_splits(len(segs), ctas, target))
+
+    def segments(segs):
+        sg = torch.tensor([(t0, c, p, i + 1) for i, (t0, c, p) in enumerate(segs)], dtype=torch.int32, device=dev)
+        if len(segs) > 1:
+            sg[:, 0] = torch.arange(len(segs), dtype=torch.int32, device=dev)
+        return sg
+
+    ctx, B, T = 4096, 64, PREFILL_TOKENS
+    n_pages = B * ctx // PAGE
+    tables = torch.randperm(n_pages, dtype=torch.int32).view(B, ctx // PAGE).to(dev)
+    cases = {"decode_b64_ctx4096": [(i, 1, ctx - 1) for i in range(B)], "prefill_2048": [(0, T, 0)]}
+    W = z["width"]
+    # -- differential attention: the two maps as heads of their own over doubled kv heads, in the window
+    H, G, dk, dv, win, taps = z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["window"], z["conv"]
+    nh, nkv = 2 * H, 2 * G
+    pool = torch.randn(n_pages, nkv, PAGE, dk + dv, device=dev).to(bf)
+    for case, segs in cases.items():
+        n = sum(c for _, c, _ in segs)
+        keys = sum(min(p + i + 1, win) for _, c, p in segs for i in range(c))
+        q, a = torch.randn(n, nh * dk, device=dev).to(bf), torch.empty(n, nh * dv, dtype=bf, device=dev)
+        w = plan(segs, ops.attention_sink_tile_tokens(nh, nkv, bf, dk, dv), ops.attention_sink_ctas_per_item(nh, nkv, bf, dk, dv), win)(nh, dv)
+        ms = timed(lambda: ops.attention_sink(q, pool, tables, w, a, None, nh, nkv, dk, dv, win, 0, dk ** -0.5, 0.0, status))
+        seg_keys = sum(min(p + c, win + c - 1) for _, c, p in segs)
+        note(f"attention_maps_{case}", ms, seg_keys * nkv * (dk + dv) * 2 + n * nh * (dk + dv) * 2, 2 * nh * (dk + dv) * keys)
+        # the maps' difference, its norm and the gate a head
+        gate, o = torch.randn(n, H, device=dev).to(bf), torch.empty(n, H * dv, dtype=bf, device=dev)
+        ms = timed(lambda: ops.diff_combine(a, gate, o, H, H // G, dv, 0.4, 0.7, 1e-6))
+        note(f"diff_combine_{case}", ms, (a.numel() + o.numel() + gate.numel()) * 2, 0)
+        # bias, convolution, rotation and the cache write
+        ch = (nh + nkv) * dk + G * dv
+        proj = torch.randn(n, ch + H, device=dev).to(bf)
+        bias, cw = torch.randn(ch, device=dev), torch.randn(ch, taps, device=dev)
+        state = torch.zeros(B + 1, ops.conv_state_floats(ch, taps), device=dev)
+        inv = torch.rand(z["rot"] // 2, device=dev)
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        slots = torch.randperm(n_pages * PAGE, dtype=torch.int32)[:n].to(dev)
+        sg = segments(segs)
+        ms = timed(lambda: ops.conv_rope_kv_write(proj, bias, cw, sg, max(c for _, c, _ in segs), state, inv, z["rot"], pos, slots, q, pool,
+                                                  nh, nkv, 2, dk, dv, status))
+        note(f"conv_rope_kv_write_{case}", ms, n * ch * 2 + n * nh * dk * 2 + n * nkv * (dk + dv) * 2 + len(segs) * state.shape[1] * 4 * 2, 0)
+    del pool
+    # -- latent attention over rows [latent | rotated key part], and the kernel that makes the rows
+    LH, ld, lr, R = z["l_heads"], z["l_dim"], z["l_rot"], z["kv_rank"]
+    width = R + lr
+    rows = torch.randn(n_pages, PAGE, width, device=dev).to(bf)
+    for case, segs in cases.items():
+        n = sum(c for _, c, _ in segs)
+        keys = sum(p + i + 1 for _, c, p in segs for i in range(c))
+        q_rows, o_rows = torch.randn(n, LH, width, device=dev).to(bf), torch.empty(n, LH, width, dtype=bf, device=dev)
+        w = plan(segs, ops.latent_attention_tile_tokens(LH, width, bf), ops.latent_attention_ctas_per_item(LH, width, bf), 0)(LH, width)
+        ms = timed(lambda: ops.latent_attention(q_rows, rows, tables, w, o_rows, 0.1, status))
+        seg_keys = sum(p + c for _, c, p in segs)
+        note(f"latent_attention_{case}", ms, seg_keys * width * 2 + 2 * n * LH * width * 2, 2 * LH * 2 * width * keys)
+        proj = torch.randn(n, LH * (ld + lr) + LH + width, device=dev).to(bf)
+        gain, inv = torch.ones(R, device=dev), torch.rand(lr // 2, device=dev)
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        slots = torch.randperm(n_pages * PAGE, dtype=torch.int32)[:n].to(dev)
+        ms = timed(lambda: ops.latent_rope_write(proj[:, LH * (ld + lr) + LH:], gain, 1e-6, proj[:, :LH * (ld + lr)], q_rows, rows, slots, pos, inv,
+                                                 LH, ld, lr, lr, R, status))
+        note(f"latent_rope_write_{case}", ms, n * (width + LH * lr) * 2 * 2, 0)
+        # its like: both latents normed and the cache row written (a q latent as wide as the rotated parts of all heads)
+        qa, cq = torch.randn(n, LH * lr + width, device=dev).to(bf), torch.empty(n, LH * lr, dtype=bf, device=dev)
+        ms = timed(lambda: ops.latent_norm_write(qa, torch.ones(LH * lr, device=dev), torch.ones(width, device=dev), 1e-6, cq, rows, slots,
+                                                 LH * lr, width, status))
+        note(f"like_latent_norm_write_{case}", ms, n * (width + LH * lr) * 2 * 2, 0)
+    del rows
+    # -- the experts: without gates, the token times its score (both forms), beside the gated ones of equal width
+    E, top, ff = z["experts"], z["top"], z["expert_ff"]
+    w_up, w_gu, w_d = (torch.randn(E, ff, W, device=dev) * 0.02).to(bf), (torch.randn(E, 2 * ff, W, device=dev) * 0.02).to(bf), \
+        (torch.randn(E, W, ff, device=dev) * 0.02).to(bf)
+    wr = torch.randn(E, W, device=dev)
+    ws_up, ws_gu = (torch.randn(z["shared_ff"], W, device=dev) * 0.02).to(bf), (torch.randn(2 * z["shared_ff"], W, device=dev) * 0.02).to(bf)
+    for case, n in (("decode_b8", 8), ("decode_b64", B), ("prefill_2048", T)):
+        h = torch.randn(n, W, device=dev).to(bf)
+        ms = timed(lambda: ops.moe_route(h, wr, None, top, 1, 1, scoring="sigmoid", renormalize=False))
+        note(f"router_sigmoid_{case}", ms, n * W * 2 + E * W * 4, 2 * n * E * W)
+        ms = timed(lambda: ops.moe_route(h, wr, None, top, 1, 1))
+        note(f"like_router_softmax_{case}", ms, n * W * 2 + E * W * 4, 2 * n * E * W)
+        ids, weights = ops.moe_route(h, wr, None, top, 1, 1, scoring="sigmoid", renormalize=False)
+        used = min(E, n * top)
+        ms = timed(lambda: ops.moe_experts(h, ids, weights, w_up, w_d, None, status, act="squared_relu", gated=False, weight_input=True))
+        note(f"experts_ungated_{case}", ms, used * 2 * ff * W * 2 + n * W * 2 * 2, 2 * n * top * 2 * ff * W)
+        ms = timed(lambda: ops.moe_experts(h, ids, weights, w_gu, w_d, None, status, act="silu"))
+        note(f"like_experts_gated_{case}", ms, used * 3 * ff * W * 2 + n * W * 2 * 2, 2 * n * top * 3 * ff * W)
+        ms = timed(lambda: ops.linear_act(h, ws_up, "squared_relu", status=status))
+        note(f"shared_up_squared_relu_{case}", ms, ws_up.numel() * 2 + n * (W + z["shared_ff"]) * 2, 2 * n * z["shared_ff"] * W)
+        ms = timed(lambda: ops.linear_glu(h, ws_gu, status=status))
+        note(f"like_shared_gate_up_silu_{case}", ms, ws_gu.numel() * 2 + n * (W + z["shared_ff"]) * 2, 2 * n * 2 * z["shared_ff"] * W)
+    return out
+
+
 TRACE_KERNELS = {0: "(tcgen05 kernel)", 1: "embed", 2: "rmsnorm", 3: "swiglu", 4: "qk_norm_rope_kv", 5: "attention_generic", 6: "attention_reduce",
                  7: "attention_mma", 8: "attention_tma", 9: "skinny_gemm", 10: "sample_partial", 11: "sample_final", 12: "gemm_tcgen05", 13: "attention_tcgen05"}
 TRACE_FILES = ["elementwise", "qk_norm_rope_kv", "attention_generic", "attention_mma", "attention_decode_tma", "sampling",
@@ -1119,7 +1341,11 @@ def main(argv=None) -> int:
     ap.add_argument("--matrix-size", choices=sorted(MATRIX_SIZES), default="1024",
                     help="with --only matrix: the width of the matrix-memory decoder (Pamarax)")
     ap.add_argument("--matrix-model", choices=["both", "pamarax", "bumisun"], default="both", help="with --only matrix: one model alone")
-    ap.add_argument("--only", choices=["decode", "prefill", "long-prompt", "timeline", "reference-kernel", "plain-cpu", "latent", "hybrid", "matrix"],
+    ap.add_argument("--tebozen-size", choices=sorted(TEBOZEN_SIZES), default="1024",
+                    help="with --only tebozen: the width of the differential-attention / matrix-LSTM / latent-attention decoder (Tebozen)")
+    ap.add_argument("--tebozen-model", choices=["both", "tebozen", "bumisun"], default="both", help="with --only tebozen: one model alone")
+    ap.add_argument("--only", choices=["decode", "prefill", "long-prompt", "timeline", "reference-kernel", "plain-cpu", "latent", "hybrid", "matrix",
+                                       "tebozen"],
                     default=None,
                     help="run one part alone and print a short line (for profiling; not a bench record); "
                          "long-prompt: a prompt of --context tokens in portions of 2048, each portion timed; "
@@ -1131,7 +1357,9 @@ def main(argv=None) -> int:
                          "clamped-experts decoder (Bumisun), with its own kernels timed alone beside the like kernels of the "
                          "Qwen3 shape (--hybrid-size, --layers, default 8); matrix: decode and prefill of the matrix-memory decoder "
                          "(Pamarax: gated attention, matrix LSTM, attention beside a gated delta rule) beside the Bumisun shape of "
-                         "equal size, with its own kernels timed alone beside Bumisun's like ones (--matrix-size, --layers, default 8)")
+                         "equal size, with its own kernels timed alone beside Bumisun's like ones (--matrix-size, --layers, default 8); "
+                         "tebozen: the same for the decoder of differential attention, matrix LSTM and latent attention layers with "
+                         "squared-relu experts (Tebozen) beside the Bumisun shape of equal size (--tebozen-size, --layers, default 8)")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -1173,6 +1401,12 @@ def main(argv=None) -> int:
     if args.only == "matrix":
         clocks.start()
         out = matrix_beside_hybrid(args.matrix_size, args.layers or 8, pk, clocks, steps, warmup, which=args.matrix_model)
+        out["clocks"] = clocks.stop()
+        print(json.dumps(out))
+        return 0
+    if args.only == "tebozen":
+        clocks.start()
+        out = tebozen_beside_hybrid(args.tebozen_size, args.layers or 8, pk, clocks, steps, warmup, which=args.tebozen_model)
         out["clocks"] = clocks.stop()
         print(json.dumps(out))
         return 0
