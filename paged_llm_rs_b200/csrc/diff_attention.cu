@@ -28,62 +28,127 @@ struct DASegment { int first, count, before, slot; };
 
 __device__ __forceinline__ float da_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// grid (segments, tokens a segment at most); one CTA a token.  conv_w float [channels, taps]; bias float [channels] or null.
-template <typename T>
+// grid (segments, chunks of `tok` tokens); conv_w float [channels, taps]; bias float [channels] or null.  A CTA stages the
+// inputs (+ bias) of its tokens and of the taps - 1 before them in shared memory, [tok + taps - 1][channels] floats, so that an
+// input is fetched once for all the taps that meet it; a thread then keeps one channel's taps (and those of the channel it is
+// rotated with) in registers and goes through the chunk's tokens.
+template <typename T, int MAXT>       // MAXT >= taps: how many taps a thread keeps in registers
 __global__ void __launch_bounds__(256) conv_rope_kv_write_kernel(
     const T* proj, int row_stride, const float* __restrict__ bias, const float* __restrict__ conv_w, int taps,
     const DASegment* __restrict__ segs, const float* state, long long state_stride,
     const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions, const int* __restrict__ slots,
     T* __restrict__ q_out, T* kv_pool, int q_heads, int k_heads, int maps, int dk, int dv, int page_size, long long pool_rows,
-    int* status) {
-    extern __shared__ float da_row[];            // the token's channels behind the convolution
+    int tok, int* status) {
+    extern __shared__ __align__(16) float da_tile[];      // [tok + taps - 1][channels], then [tok][rot / 2] cosines and as many sines
+    __shared__ long long base_s[32];                      // where a token's rows begin in the pool (kv head 0), or -1
     pdl_launch_dependents();
     pdl_wait(KID_DIFF);
     const DASegment s = segs[blockIdx.x];
-    const int t = blockIdx.y;
-    if (t >= s.count) return;
-    const int token = s.first + t;
+    const int t0 = blockIdx.y * tok;
+    if (t0 >= s.count) return;
+    const int nt = min(tok, s.count - t0);
     const int cq = q_heads * dk, ck = k_heads * dk, cv = (k_heads / maps) * dv;
     const int channels = cq + ck + cv;
+    const int row_w = dk + dv;
     const float* st = state + (size_t)s.slot * state_stride;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        const float b = bias ? bias[c] : 0.f;
-        float acc = 0.f;
-        for (int j = 0; j < taps; j++) {
-            const int r = t - (taps - 1) + j;          // relative to the segment's first token
-            float x;
-            if (r >= 0) x = to_f32(proj[(size_t)(s.first + r) * row_stride + c]) + b;
-            else x = s.before > 0 ? st[(size_t)(taps - 1 + r) * channels + c] : 0.f;
-            acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
+    if (threadIdx.x < nt) {
+        const int token = s.first + t0 + threadIdx.x;
+        const int slot = (kv_pool && slots) ? slots[token] : -1;
+        if (slot >= pool_rows) atomicOr(status, 2);
+        base_s[threadIdx.x] = (slot >= 0 && slot < pool_rows)
+            ? ((long long)(slot / page_size) * k_heads * page_size + slot % page_size) * row_w : -1;
+    }
+    const int rows = nt + taps - 1;
+    const int half = rot / 2;
+    // a token's angles are the same for every head: formed once a token and pair
+    float* cos_s = da_tile + (size_t)(tok + taps - 1) * channels;
+    float* sin_s = cos_s + tok * half;
+    for (int idx = threadIdx.x; idx < nt * half; idx += blockDim.x) {
+        float sn, cs;
+        sincosf((float)positions[s.first + t0 + idx / half] * inv_freq[idx % half], &sn, &cs);
+        cos_s[idx] = cs; sin_s[idx] = sn;
+    }
+    constexpr int N = Vec16<T>::N;
+    if (channels % N == 0 && row_stride % N == 0 && ((uintptr_t)proj & 15) == 0) {
+        const int vec_per_row = channels / N;
+        for (int idx = threadIdx.x; idx < rows * vec_per_row; idx += blockDim.x) {
+            const int rr = idx / vec_per_row, c = (idx % vec_per_row) * N;
+            const int r = t0 - (taps - 1) + rr;        // relative to the segment's first token
+            float f[N];
+            if (r >= 0) {
+                Vec16<T> v; v.load(proj + (size_t)(s.first + r) * row_stride + c); v.unpack(f);
+                if (bias) {
+#pragma unroll
+                    for (int k = 0; k < N; k += 4) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(bias + c + k);
+                        f[k] += b4.x; f[k + 1] += b4.y; f[k + 2] += b4.z; f[k + 3] += b4.w;
+                    }
+                }
+            } else if (s.before > 0) {
+#pragma unroll
+                for (int k = 0; k < N; k += 4) {
+                    const float4 o4 = *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 + r) * channels + c + k);
+                    f[k] = o4.x; f[k + 1] = o4.y; f[k + 2] = o4.z; f[k + 3] = o4.w;
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < N; k++) f[k] = 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < N; k += 4)
+                *reinterpret_cast<float4*>(da_tile + (size_t)rr * channels + c + k) = make_float4(f[k], f[k + 1], f[k + 2], f[k + 3]);
         }
-        da_row[c] = acc;
+    } else {
+        for (int idx = threadIdx.x; idx < rows * channels; idx += blockDim.x) {
+            const int rr = idx / channels, c = idx % channels;
+            const int r = t0 - (taps - 1) + rr;
+            da_tile[idx] = r >= 0 ? to_f32(proj[(size_t)(s.first + r) * row_stride + c]) + (bias ? bias[c] : 0.f)
+                                  : (s.before > 0 ? st[(size_t)(taps - 1 + r) * channels + c] : 0.f);
+        }
     }
     __syncthreads();
-    const float pos = (float)positions[token];
-    const int half = rot / 2;
-    const int slot = (kv_pool && slots) ? slots[token] : -1;
-    const bool writes = slot >= 0 && slot < pool_rows;
-    if (slot >= pool_rows && threadIdx.x == 0) atomicOr(status, 2);
-    const int row_w = dk + dv;
-    for (int i = threadIdx.x; i < cq + ck; i += blockDim.x) {
-        const int e = i % dk;
-        float y = da_row[i];
-        if (e < rot) {
-            float sn, cs;
-            sincosf(pos * inv_freq[e % half], &sn, &cs);
-            y = e < half ? y * cs - da_row[i + half] * sn : y * cs + da_row[i - half] * sn;
+    const long long head_stride = (long long)page_size * row_w;      // from a kv head's rows of a page to the next one's
+    for (int i = threadIdx.x; i < channels; i += blockDim.x) {
+        // what does not depend on the token: the channel's place in its head, the channel it is turned with, its taps, and
+        // where it goes in a token's rows
+        const bool is_q = i < cq, is_v = i >= cq + ck;
+        const int within = is_v ? i - cq - ck : (is_q ? i : i - cq);
+        const int head = within / (is_v ? dv : dk), e = within - head * (is_v ? dv : dk);
+        const bool turned = !is_v && e < rot;
+        const int eh = turned ? (e < half ? e : e - half) : 0;
+        const int partner = turned ? (e < half ? i + half : i - half) : i;
+        const float sign = e < half ? -1.f : 1.f;
+        const long long off = is_v ? (long long)head * maps * head_stride + dk + e : (long long)head * head_stride + e;
+        float wi[MAXT], wp[MAXT];
+#pragma unroll
+        for (int j = 0; j < MAXT; j++) {
+            wi[j] = j < taps ? conv_w[(size_t)i * taps + j] : 0.f;
+            wp[j] = (turned && j < taps) ? conv_w[(size_t)partner * taps + j] : 0.f;
         }
-        if (i < cq) q_out[(size_t)token * cq + i] = from_f32<T>(y);
-        else if (writes) {
-            const int head = (i - cq) / dk;
-            kv_pool[(((size_t)(slot / page_size) * k_heads + head) * page_size + slot % page_size) * row_w + e] = from_f32<T>(y);
+        const float* mine = da_tile + i;
+        const float* other = da_tile + partner;
+        T* qdst = q_out + (size_t)(s.first + t0) * cq + i;
+        for (int t = 0; t < nt; t++) {
+            float y = 0.f, yp = 0.f;
+#pragma unroll
+            for (int j = 0; j < MAXT; j++) {        // (taps beyond the convolution's have weight zero and meet the tile's own rows)
+                if (j < taps) {
+                    y = fmaf(wi[j], mine[(size_t)(t + j) * channels], y);
+                    yp = fmaf(wp[j], other[(size_t)(t + j) * channels], yp);
+                }
+            }
+            if (turned) y = y * cos_s[t * half + eh] + sign * yp * sin_s[t * half + eh];
+            const T out = from_f32<T>(y);
+            if (is_q) qdst[(size_t)t * cq] = out;
+            else {
+                const long long base = base_s[t];
+                if (base >= 0) {
+                    if (!is_v) kv_pool[base + off] = out;
+                    else
+                        for (int z = 0; z < maps; z++) kv_pool[base + off + z * head_stride] = out;      // behind every map's key
+                }
+            }
         }
-    }
-    if (!writes) return;
-    for (int i = threadIdx.x; i < k_heads * dv; i += blockDim.x) {
-        const int head = i / dv, e = i % dv;
-        kv_pool[(((size_t)(slot / page_size) * k_heads + head) * page_size + slot % page_size) * row_w + dk + e] =
-            from_f32<T>(da_row[cq + ck + (head / maps) * dv + e]);
     }
 }
 
@@ -119,18 +184,32 @@ PLLM_EXPORT int pllm_conv_rope_kv_write(int dtype, const void* proj, int row_str
         return PLLM_ERR_SIZE;
     if (rot < 0 || rot % 2 || rot > dk || (rot > 0 && !inv_freq)) return PLLM_ERR_SIZE;
     const int channels = (q_heads + k_heads) * dk + (k_heads / maps) * dv;
-    const size_t smem = (size_t)channels * sizeof(float);
-    if (smem > 200 * 1024) return PLLM_ERR_LIMIT;
-    if (max_segment_tokens > 65535) return PLLM_ERR_LIMIT;
+    // tokens a CTA: what some 56 KB of shared memory hold beside the taps - 1 rows before them (four CTAs an SM: the kernel is
+    // bound by latency, and an input that two CTAs stage comes from L2 the second time), 32 at most
+    const size_t row_bytes = (size_t)channels * sizeof(float);
+    if (row_bytes * taps + (size_t)rot * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
+    const int fit = (int)((size_t)(56 * 1024) / row_bytes);      // rows of the tile
+    int tok = max(1, min(32, fit - (taps - 1)));
+    tok = min(tok, max_segment_tokens);
+    const size_t smem = row_bytes * (tok + taps - 1) + (size_t)tok * rot * sizeof(float);
+    const int chunks = (max_segment_tokens + tok - 1) / tok;
+    if (chunks > 65535) return PLLM_ERR_LIMIT;
+#define DA_LAUNCH(MAXT)                                                                                                          \
+    do {                                                                                                                         \
+        cudaFuncSetAttribute(conv_rope_kv_write_kernel<T, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+        launch_chained(conv_rope_kv_write_kernel<T, MAXT>, dim3(n_segs, chunks), dim3(256), smem, stream, (const T*)proj,        \
+                       row_stride, bias, conv_w, taps, (const DASegment*)segs, (const float*)state, state_stride, inv_freq, rot, \
+                       positions, slots, (T*)q_out, (T*)kv_pool, q_heads, k_heads, maps, dk, dv, page_size, pool_rows, tok,      \
+                       status);                                                                                                  \
+    } while (0)
     PLLM_DISPATCH_DTYPE(dtype, {
-        cudaFuncSetAttribute(conv_rope_kv_write_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_chained(conv_rope_kv_write_kernel<T>, dim3(n_segs, max_segment_tokens), dim3(256), smem, stream, (const T*)proj,
-                       row_stride, bias, conv_w, taps, (const DASegment*)segs, (const float*)state, state_stride, inv_freq, rot,
-                       positions, slots, (T*)q_out, (T*)kv_pool, q_heads, k_heads, maps, dk, dv, page_size, pool_rows, status);
+        if (taps <= 4) DA_LAUNCH(4);
+        else DA_LAUNCH(DA_MAX_TAPS);
         if (taps > 1)
             launch_chained(conv_state_update_kernel<T>, dim3(n_segs, (channels + 255) / 256), dim3(256), 0, stream, (const T*)proj,
                            row_stride, bias, taps, (const DASegment*)segs, state, state_stride, channels);
     });
+#undef DA_LAUNCH
     return launch_status();
 }
 

@@ -146,6 +146,9 @@ __global__ void __launch_bounds__(16 * 32, 1) skinny_gemm_kernel(const bf16* x, 
                 const float g = __bfloat162float(__float2bfloat16_rn(s));
                 u = __bfloat162float(__float2bfloat16_rn(u));
                 s = glu_act(act, limit, g, u);
+            } else if (act != UNARY_NONE) {
+                // (plain product: `act` names a one-argument activation of the product, rounded first as a product of its own would leave it)
+                s = unary_act(act, __bfloat162float(__float2bfloat16_rn(s)));
             }
             y[(size_t)m * N + n0 + c] = from_f32<OutT>(s);
         }
@@ -156,6 +159,10 @@ __global__ void __launch_bounds__(16 * 32, 1) skinny_gemm_kernel(const bf16* x, 
             for (int b = 0; b < NT; b++) {
                 const int c = n0 + b * 8 + t * 2;
                 const int m0 = a * 16 + r, m1 = m0 + 8;
+                if (act != UNARY_NONE) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) acc[a][b][q] = unary_act(act, __bfloat162float(__float2bfloat16_rn(acc[a][b][q])));
+                }
                 if (m0 < M) { y[(size_t)m0 * N + c] = from_f32<OutT>(acc[a][b][0]); y[(size_t)m0 * N + c + 1] = from_f32<OutT>(acc[a][b][1]); }
                 if (m1 < M) { y[(size_t)m1 * N + c] = from_f32<OutT>(acc[a][b][2]); y[(size_t)m1 * N + c + 1] = from_f32<OutT>(acc[a][b][3]); }
             }
@@ -198,11 +205,11 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
 }
 
 template <int NT, typename OutT>
-static int pick_mt(const void* x, const void* w, void* y, int M, int N, int K, int warps, cudaStream_t s) {
-    if (M <= 16) return launch_skinny<1, NT, 0, OutT>(x, w, y, M, N, K, warps, s);
-    if (M <= 32) return launch_skinny<2, NT, 0, OutT>(x, w, y, M, N, K, warps, s);
-    if (M <= 48) return launch_skinny<3, NT, 0, OutT>(x, w, y, M, N, K, warps, s);
-    return launch_skinny<4, NT, 0, OutT>(x, w, y, M, N, K, warps, s);
+static int pick_mt(const void* x, const void* w, void* y, int M, int N, int K, int warps, cudaStream_t s, int act) {
+    if (M <= 16) return launch_skinny<1, NT, 0, OutT>(x, w, y, M, N, K, warps, s, act);
+    if (M <= 32) return launch_skinny<2, NT, 0, OutT>(x, w, y, M, N, K, warps, s, act);
+    if (M <= 48) return launch_skinny<3, NT, 0, OutT>(x, w, y, M, N, K, warps, s, act);
+    return launch_skinny<4, NT, 0, OutT>(x, w, y, M, N, K, warps, s, act);
 }
 
 // K is split over the warps of a CTA.  A warp's loads of ``slice`` values of k are all
@@ -221,10 +228,11 @@ static int pick_warps(int K, int ctas, int slice, int warps_an_sm = 64, int max_
     return warps;
 }
 
-// x: [M, K]; w: [N, K]; y: [M, N] bfloat16 (out_f32 0) or float (out_f32 1).
-PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, int N, int K, int out_f32,
-                                 cudaStream_t stream) {
-    if (!pllm_skinny_gemm_supports(M, N, K)) return PLLM_ERR_SIZE;
+// x: [M, K]; w: [N, K]; y: [M, N] bfloat16 (out_f32 0) or float (out_f32 1); act: a one-argument activation of the product
+// (UNARY_*, common.cuh), UNARY_NONE for the product itself.
+PLLM_EXPORT int pllm_skinny_gemm_act(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int act,
+                                     cudaStream_t stream) {
+    if (!pllm_skinny_gemm_supports(M, N, K) || act < UNARY_NONE || act > UNARY_RELU2) return PLLM_ERR_SIZE;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return PLLM_ERR_ALIGN;
     // More than 16 rows: tiles of 16 rows of W while that still gives every SM several CTAs, else of 8.
     const int sms = sm_count();
@@ -253,11 +261,15 @@ PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, i
     if (g_skinny_nt_override && N % (8 * g_skinny_nt_override) == 0 && (g_skinny_nt_override < 4 || M <= 16)) nt = g_skinny_nt_override;
     const int warps = pick_warps(K, N / (8 * nt), 128, warps_an_sm, max_warps);
     if (nt == 4)
-        return out_f32 ? launch_skinny<1, 4, 0, float>(x, w, y, M, N, K, warps, stream)
-                       : launch_skinny<1, 4, 0, bf16>(x, w, y, M, N, K, warps, stream);
+        return out_f32 ? launch_skinny<1, 4, 0, float>(x, w, y, M, N, K, warps, stream, act)
+                       : launch_skinny<1, 4, 0, bf16>(x, w, y, M, N, K, warps, stream, act);
     if (out_f32)
-        return nt == 2 ? pick_mt<2, float>(x, w, y, M, N, K, warps, stream) : pick_mt<1, float>(x, w, y, M, N, K, warps, stream);
-    return nt == 2 ? pick_mt<2, bf16>(x, w, y, M, N, K, warps, stream) : pick_mt<1, bf16>(x, w, y, M, N, K, warps, stream);
+        return nt == 2 ? pick_mt<2, float>(x, w, y, M, N, K, warps, stream, act) : pick_mt<1, float>(x, w, y, M, N, K, warps, stream, act);
+    return nt == 2 ? pick_mt<2, bf16>(x, w, y, M, N, K, warps, stream, act) : pick_mt<1, bf16>(x, w, y, M, N, K, warps, stream, act);
+}
+
+PLLM_EXPORT int pllm_skinny_gemm(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, cudaStream_t stream) {
+    return pllm_skinny_gemm_act(x, w, y, M, N, K, out_f32, UNARY_NONE, stream);
 }
 
 // w is [2N, K], gate rows then up rows, and y[M, N] = silu(x Wg^T) * (x Wu^T); up to 16 rows, all bfloat16.

@@ -49,6 +49,7 @@ def lib():
             "pllm_sample_scratch_floats": [c_int, c_int],
             "pllm_skinny_gemm_supports": [c_int, c_int, c_int],
             "pllm_skinny_gemm": [P, P, P, c_int, c_int, c_int, c_int, P],
+            "pllm_skinny_gemm_act": [P, P, P, c_int, c_int, c_int, c_int, c_int, P],
             "pllm_skinny_gemm_glu_supports": [c_int, c_int, c_int],
             "pllm_skinny_gemm_glu": [P, P, P, c_int, c_int, c_int, c_int, c_float, P],
             "pllm_sm_count": [],
@@ -1322,13 +1323,20 @@ def unary_act(x: torch.Tensor, act: str) -> torch.Tensor:
 
 
 def linear_act(x: torch.Tensor, weight: torch.Tensor, act: str, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """act(x W^T) for a one-argument activation: the first half of a feed-forward without a gate.  Many rows in bfloat16:
-    the tcgen05 product with the activation in its epilogue; otherwise the product, then the activation in place."""
+    """act(x W^T) for a one-argument activation: the first half of a feed-forward without a gate.  In bfloat16 the
+    activation sits in the epilogue of the weight-streaming product (few rows) or of the tcgen05 product (many rows);
+    otherwise the product, then the activation in place."""
     if act not in UNARY_KINDS:
         raise KernelError(f"linear_act: activation {act!r} is not known; known: {sorted(UNARY_KINDS)}")
     N, K = weight.shape
     if x.shape[-1] != K:
         raise KernelError(f"linear_act: input width {x.shape[-1]} does not fit a weight of {tuple(weight.shape)}")
+    if skinny_gemm_takes(x, weight, K) and N <= SKINNY_MAX_N:
+        _dev(x, weight)
+        out = torch.empty((x.shape[0], N), dtype=torch.bfloat16, device=x.device)
+        _check(lib().pllm_skinny_gemm_act(_ptr(x), _ptr(weight), _ptr(out), x.shape[0], N, K, 0, UNARY_KINDS[act], _stream()),
+               "skinny_gemm (activation)")
+        return out
     if TCGEN05_GEMM >= 1 and x.shape[0] >= TCGEN05_MIN_M and gemm_tcgen05_takes(x, weight, N, False):
         _dev(x, weight)
         out = torch.empty((x.shape[0], N), dtype=torch.bfloat16, device=x.device)
