@@ -33,7 +33,7 @@ __device__ __forceinline__ float da_sigmoid(float z) { return 1.0f / (1.0f + exp
 // input is fetched once for all the taps that meet it; a thread then keeps one channel's taps (and those of the channel it is
 // rotated with) in registers and goes through the chunk's tokens.
 template <typename T, int MAXT>       // MAXT >= taps: how many taps a thread keeps in registers
-__global__ void __launch_bounds__(256) conv_rope_kv_write_kernel(
+__global__ void __launch_bounds__(512) conv_rope_kv_write_kernel(
     const T* proj, int row_stride, const float* __restrict__ bias, const float* __restrict__ conv_w, int taps,
     const DASegment* __restrict__ segs, const float* state, long long state_stride,
     const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions, const int* __restrict__ slots,
@@ -184,12 +184,12 @@ PLLM_EXPORT int pllm_conv_rope_kv_write(int dtype, const void* proj, int row_str
         return PLLM_ERR_SIZE;
     if (rot < 0 || rot % 2 || rot > dk || (rot > 0 && !inv_freq)) return PLLM_ERR_SIZE;
     const int channels = (q_heads + k_heads) * dk + (k_heads / maps) * dv;
-    // tokens a CTA: what some 56 KB of shared memory hold beside the taps - 1 rows before them (four CTAs an SM: the kernel is
-    // bound by latency, and an input that two CTAs stage comes from L2 the second time), 32 at most
+    // tokens a CTA: what some 100 KB of shared memory hold beside the taps - 1 rows before them (two CTAs of sixteen warps an
+    // SM), 16 at most: what a thread works out for its channel is then shared by several tokens
     const size_t row_bytes = (size_t)channels * sizeof(float);
     if (row_bytes * taps + (size_t)rot * sizeof(float) > 200 * 1024) return PLLM_ERR_LIMIT;
-    const int fit = (int)((size_t)(56 * 1024) / row_bytes);      // rows of the tile
-    int tok = max(1, min(32, fit - (taps - 1)));
+    const int fit = (int)((size_t)(100 * 1024) / row_bytes);      // rows of the tile
+    int tok = max(1, min(16, fit - (taps - 1)));
     tok = min(tok, max_segment_tokens);
     const size_t smem = row_bytes * (tok + taps - 1) + (size_t)tok * rot * sizeof(float);
     const int chunks = (max_segment_tokens + tok - 1) / tok;
@@ -197,7 +197,7 @@ PLLM_EXPORT int pllm_conv_rope_kv_write(int dtype, const void* proj, int row_str
 #define DA_LAUNCH(MAXT)                                                                                                          \
     do {                                                                                                                         \
         cudaFuncSetAttribute(conv_rope_kv_write_kernel<T, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        launch_chained(conv_rope_kv_write_kernel<T, MAXT>, dim3(n_segs, chunks), dim3(256), smem, stream, (const T*)proj,        \
+        launch_chained(conv_rope_kv_write_kernel<T, MAXT>, dim3(n_segs, chunks), dim3(512), smem, stream, (const T*)proj,        \
                        row_stride, bias, conv_w, taps, (const DASegment*)segs, (const float*)state, state_stride, inv_freq, rot, \
                        positions, slots, (T*)q_out, (T*)kv_pool, q_heads, k_heads, maps, dk, dv, page_size, pool_rows, tok,      \
                        status);                                                                                                  \
